@@ -5,10 +5,12 @@ from .lfm2 import Lfm2Config
 from .plan import (
     AttentionSpec,
     BlockSpec,
+    DenseMLPSpec,
     FeedForwardSpec,
     GatedDeltaSpec,
     GatedMLPSpec,
     LatentAttentionSpec,
+    LayerNormSpec,
     MixerSpec,
     ModelPlan,
     NormSpec,
@@ -21,23 +23,29 @@ from .plan import (
     SandwichBlockSpec,
     ScheduleEntry,
     ShortConvSpec,
+    StreamMixSpec,
+    YarnScaling,
 )
 from .tudulix import TudulixConfig
+from .vivulorn import VivulornConfig
 from .vuvulorn import VuvulornConfig
 from .registry import architectures, config_from_dict, load_config, register_architecture
 
 register_architecture("Lfm2ForCausalLM", Lfm2Config)
 register_architecture("Vuvulorn", VuvulornConfig)
 register_architecture("Tudulix", TudulixConfig)
+register_architecture("Vivulorn", VivulornConfig)
 
 __all__ = [
     "AttentionSpec",
     "BlockSpec",
     "ConfigError",
+    "DenseMLPSpec",
     "FeedForwardSpec",
     "GatedDeltaSpec",
     "GatedMLPSpec",
     "LatentAttentionSpec",
+    "LayerNormSpec",
     "Lfm2Config",
     "MixerSpec",
     "ModelPlan",
@@ -51,9 +59,12 @@ __all__ = [
     "SandwichBlockSpec",
     "ScheduleEntry",
     "ShortConvSpec",
+    "StreamMixSpec",
     "TudulixConfig",
     "UnknownArchitectureError",
+    "VivulornConfig",
     "VuvulornConfig",
+    "YarnScaling",
     "architectures",
     "config_from_dict",
     "load_config",

@@ -19,12 +19,14 @@ from typing import ClassVar
 __all__ = [
     "AttentionSpec",
     "BlockSpec",
+    "DenseMLPSpec",
     "EmbeddingSpec",
     "HeadSpec",
     "FeedForwardSpec",
     "GatedDeltaSpec",
     "GatedMLPSpec",
     "LatentAttentionSpec",
+    "LayerNormSpec",
     "MixerSpec",
     "ModelPlan",
     "NormSpec",
@@ -37,6 +39,8 @@ __all__ = [
     "SandwichBlockSpec",
     "ScheduleEntry",
     "ShortConvSpec",
+    "StreamMixSpec",
+    "YarnScaling",
 ]
 
 
@@ -65,8 +69,32 @@ class RMSNormSpec(NormSpec):
 
 
 @dataclass(frozen=True)
+class LayerNormSpec(NormSpec):
+    """Layer norm with weight and bias: ``(x - mean) / sqrt(var + eps) * w + b``, the variance being the mean of the
+    squared deviations; 32-bit throughout, rounded once to the activation type."""
+
+    kind: ClassVar[str] = "layer_norm"
+    dim: int = 0
+    eps: float = 1e-5
+
+
+@dataclass(frozen=True)
 class PositionSpec:
     kind: ClassVar[str] = "abstract"
+
+
+@dataclass(frozen=True)
+class YarnScaling:
+    """Frequencies stretched for contexts beyond the ``original`` one: pair ``i`` of ``n`` rotated channels turns
+    ``original * f_i / (2 pi)`` times within the original context; with ``pair(t) = n ln(original / (2 pi t)) / (2 ln theta)``
+    the pair that turns ``t`` times, ``lo = max(floor(pair(fast)), 0)``, ``hi = min(ceil(pair(slow)), n - 1)`` and
+    ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, the frequency becomes ``f_i / factor * ramp_i + f_i (1 - ramp_i)``,
+    and sines and cosines are multiplied by ``0.1 ln(factor) + 1``."""
+
+    factor: float = 1.0
+    original: float = 0.0
+    fast: float = 32.0
+    slow: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -80,6 +108,7 @@ class RopeSpec(PositionSpec):
     rotary_dim: int = 0
     theta: float = 10000.0
     pairing: str = "half"
+    scaling: YarnScaling | None = None  # stretched frequencies and a factor on sines and cosines
 
 
 @dataclass(frozen=True)
@@ -104,6 +133,11 @@ class AttentionSpec(MixerSpec):
     value_dim: int | None = None  # size of a value head; None -> head_dim
     keep_first: int = 0  # under a window, the first tokens of a request that stay visible (at their true positions)
     has_bias: bool = False  # biases on the q, k, v and output projections
+    # ``qk_norm`` over all rows of the q projection (and of the k projection) at once, before they are split into heads
+    # (its ``dim`` is then ``head_dim`` still; the weights have one element per row of the projection); 32-bit, no rounding
+    # between the norm and the rotation.
+    qk_norm_whole: bool = False
+    gated: bool = False  # the concatenated heads are multiplied by ``sigmoid(W_gate h)`` before the out-projection
 
 
 @dataclass(frozen=True)
@@ -127,6 +161,7 @@ class LatentAttentionSpec(MixerSpec):
     window: int | None = None
     scale: float | None = None  # None -> (head_dim + rope_dim) ** -0.5
     gated: bool = False
+    sink: bool = False  # a learned number per head whose exponential joins the softmax's denominator (no key, no value, not scaled)
 
 
 @dataclass(frozen=True)
@@ -138,7 +173,11 @@ class GatedDeltaSpec(MixerSpec):
     (``x / sqrt(sum x^2 + unit_eps)``, q times ``key_dim ** -0.5``); ``beta = sigmoid(W_b h)``;
     ``g = exp(-exp(A_log) softplus(W_a2 W_a1 h + dt_bias))`` through a bottleneck of ``decay_rank``; the
     read-out is RMS-normed per head (``norm_eps``) and multiplied by ``sigmoid(W_g2 W_g1 h)`` through a
-    bottleneck of ``gate_rank``, then projected out."""
+    bottleneck of ``gate_rank``, then projected out.
+
+    ``decay_per_channel=False``: one decay per head, ``g = exp(-exp(A_log) softplus(W_a h + dt_bias))`` with one row of
+    ``W_a`` and one ``dt_bias`` per head.  ``decay_rank=0`` / ``gate_rank=0``: no bottleneck, the logits are a plain
+    projection of the mixer's input.  ``gate_activation``: ``"sigmoid"`` or ``"silu"``."""
 
     kind: ClassVar[str] = "gated_delta"
     model_dim: int = 0
@@ -151,6 +190,8 @@ class GatedDeltaSpec(MixerSpec):
     gate_rank: int = 0
     norm_eps: float = 1e-6
     unit_eps: float = 1e-6
+    decay_per_channel: bool = True
+    gate_activation: str = "sigmoid"
 
 
 @dataclass(frozen=True)
@@ -188,6 +229,18 @@ class GatedMLPSpec(FeedForwardSpec):
     hidden_dim: int = 0
     activation: str = "silu"
     limit: float = 0.0  # of the "sigmoid_limit" activation
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec(FeedForwardSpec):
+    """``down(act(up(x) + b_up)) + b_down``: two projections, no gate.  ``activation``: ``"gelu"`` (the exact gelu,
+    ``0.5 z (1 + erf(z / sqrt 2))``), ``"silu"`` or ``"identity"``."""
+
+    kind: ClassVar[str] = "dense_mlp"
+    model_dim: int = 0
+    hidden_dim: int = 0
+    activation: str = "gelu"
+    has_bias: bool = True
 
 
 @dataclass(frozen=True)
@@ -246,12 +299,12 @@ class SandwichBlockSpec:
 @dataclass(frozen=True)
 class BlockSpec:
     """Pre-norm residual block: ``h = x + mixer(norm1(x)); y = h + ffn(norm2(h))``
-    (``lalamo/modules/transformer_layer.py:220-377``)."""
+    (``lalamo/modules/transformer_layer.py:220-377``); ``ffn=None`` (with ``pre_ffn_norm=None``): no second half."""
 
     pre_mixer_norm: NormSpec
     mixer: MixerSpec
-    pre_ffn_norm: NormSpec
-    ffn: FeedForwardSpec
+    pre_ffn_norm: NormSpec | None = None
+    ffn: FeedForwardSpec | None = None
     arrangement: str = "pre_norm"
 
 
@@ -275,6 +328,17 @@ class HeadSpec:
     model_dim: int = 0
     tied: bool = True
     scale: float = 1.0  # the logits are multiplied by this (in 32-bit)
+    softcap: float = 0.0  # > 0: the logits become ``softcap * tanh(logits / softcap)`` (in 32-bit, after the scale)
+
+
+@dataclass(frozen=True)
+class StreamMixSpec:
+    """A projection that renews the residual stream from itself and the embedding's output: ``x <- W [x ; x0]`` with
+    ``W [model_dim, 2 model_dim]`` (the stream's columns first) and ``x0`` the stream as the embedding left it.  Schedule
+    entries with ``mix_embedding`` run it right before their block."""
+
+    kind: ClassVar[str] = "stream_mix"
+    model_dim: int = 0
 
 
 @dataclass(frozen=True)
@@ -292,6 +356,9 @@ class ScheduleEntry:
     # True: the embedding's output (the stream as it was before the first block) is added to the stream
     # right before this execution (a model that runs a stretch of its layers several times re-feeds its input).
     add_embedding: bool = False
+    # True: the stream is renewed from itself and the embedding's output by the plan's ``stream_mix`` projection
+    # right before this execution (see :class:`StreamMixSpec`).
+    mix_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -308,6 +375,7 @@ class ModelPlan:
     # capped logits gives a specification of its own, for which a part is registered.
     embedding: EmbeddingSpec | None = None
     head: HeadSpec | None = None
+    stream_mix: StreamMixSpec | None = None  # needed by schedule entries with ``mix_embedding``
 
     def __post_init__(self) -> None:
         if self.embedding is None:
@@ -321,6 +389,8 @@ class ModelPlan:
         for position, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule[{position}] names layer {entry.layer}, but there are {len(self.layers)}")
+            if entry.mix_embedding and self.stream_mix is None:
+                raise ValueError(f"schedule[{position}] mixes the embedding into the stream, but the plan has no stream_mix")
             if entry.cache_from is not None and not 0 <= entry.cache_from < position:
                 raise ValueError(
                     f"schedule[{position}].cache_from={entry.cache_from} must name an earlier schedule entry"

@@ -103,7 +103,8 @@ constexpr int kLatentThreads = 128, kLatentChunk = 128, kLatentMaxDimsPerThread 
 template <typename T>
 __global__ void latent_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* __restrict__ out, const int* __restrict__ positions,
                                               const int* __restrict__ token_segment, const int* __restrict__ block_table, LatentLayout layout, int num_heads,
-                                              float scale, int window, int* status) {
+                                              float scale, int window, int* status, const float* __restrict__ sink) {
+    // sink (may be null): one number per head whose exponential joins the denominator; it has no row and is not scaled.
     extern __shared__ __align__(16) float shared[];
     const int latent = layout.latent, full = layout.latent + layout.rope;
     const T** rows = reinterpret_cast<const T**>(shared);                       // kLatentChunk pointers
@@ -168,6 +169,18 @@ __global__ void latent_attention_plain_kernel(const T* __restrict__ q, const T* 
         __syncthreads();   // scores[] and rows[] are rewritten by the next chunk
     }
     T* dst = out + (static_cast<size_t>(token) * num_heads + head) * latent;
+    if (sink != nullptr) {
+        // sum_j e^(s_j - m) + e^(sink - m), with both scaled by e^(m - sink) where the sink is the larger
+        const float gap = sink[head] - running_max;
+        if (gap > 0.0f) {
+            const float shrink = expf(-gap);
+#pragma unroll
+            for (int slot = 0; slot < kLatentMaxDimsPerThread; ++slot) acc[slot] *= shrink;
+            running_sum = running_sum * shrink + 1.0f;
+        } else {
+            running_sum += expf(gap);
+        }
+    }
     const float norm = running_sum > 0.0f ? 1.0f / running_sum : 0.0f;
 #pragma unroll
     for (int slot = 0; slot < kLatentMaxDimsPerThread; ++slot) {
@@ -216,6 +229,7 @@ struct LatentMmaParams {
     int num_heads, heads_per_cta, tokens_per_cta, head_blocks, splits, window;
     float scale_log2;
     int* status;
+    const float* sink;            // [heads] or null: a number per head whose exponential joins the denominator (not scaled)
 };
 
 __device__ __forceinline__ void latent_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -469,7 +483,13 @@ latent_attention_mma_kernel(LatentMmaParams p) {
         const int token = first_token + row / heads_here, head = head0 + row % heads_here;
         const float sum = half == 0 ? sum_a : sum_b, top = half == 0 ? max_a : max_b;
         if (p.splits == 1) {
-            const float norm = sum > 0.0f ? 1.0f / sum : 0.0f;
+            float norm = sum > 0.0f ? 1.0f / sum : 0.0f;
+            if (p.sink != nullptr) {
+                // sum is relative to the largest score: sum_j 2^((s_j - top) scale_log2); the sink joins it as 2^(sink log2 e - top scale_log2),
+                // computed on the side that cannot overflow
+                const float gap = p.sink[head] * 1.4426950408889634f - (top == -INFINITY ? 0.0f : top * p.scale_log2);
+                norm = top == -INFINITY ? 0.0f : (gap > 0.0f ? exp2f(-gap) / (sum * exp2f(-gap) + 1.0f) : 1.0f / (sum + exp2f(gap)));
+            }
             __nv_bfloat16* dst = p.out + (static_cast<size_t>(token) * p.num_heads + head) * latent + chunk0;
 #pragma unroll
             for (int j = 0; j < kLatentMmaChunk / 8; ++j)
@@ -489,7 +509,8 @@ latent_attention_mma_kernel(LatentMmaParams p) {
 
 // out[token][head] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over the splits, in split order.  One block per (token, head);
 // shared memory: a float per split.
-__global__ void latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int splits, int latent) {
+__global__ void latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int splits, int latent,
+                                    const float* __restrict__ sink, int num_heads) {
     extern __shared__ float split_weight[];
     const size_t row = blockIdx.x;
     const float* mine = partial + row * splits * (latent + 2);
@@ -497,13 +518,16 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial, __nv_bflo
         float top = -INFINITY;
         for (int s = threadIdx.x; s < splits; s += 32) top = fmaxf(top, mine[s * (latent + 2) + latent]);
         top = warp_max(top);
+        // the sink (a number per head, base e, joined to the denominator once) counts as one more split with sum 1 and no rows
+        const float sink_top = sink != nullptr ? sink[row % num_heads] * 1.4426950408889634f : -INFINITY;
+        top = fmaxf(top, sink_top);
         for (int s = threadIdx.x; s < splits; s += 32) {
             const float m = mine[s * (latent + 2) + latent];
             split_weight[s] = m == -INFINITY ? 0.0f : exp2f(m - top);
         }
         __syncwarp();
         if (threadIdx.x == 0) {
-            float total = 0.0f;
+            float total = sink != nullptr ? exp2f(sink_top - top) : 0.0f;
             for (int s = 0; s < splits; ++s) total += split_weight[s] * mine[s * (latent + 2) + latent + 1];   // in split order
             const float norm = total > 0.0f ? 1.0f / total : 0.0f;
             for (int s = 0; s < splits; ++s) split_weight[s] *= norm;
@@ -640,7 +664,7 @@ int lb_latent_prepare(const void* q, int q_stride, const void* q_latent, const v
 
 int lb_latent_attention_plain(const void* q, const void* pages, void* out, const int* positions, const int* token_segment, const int* block_table,
                               int tokens, int num_heads, int latent, int rope, int page_size, int num_pages, int max_blocks, float scale, int window,
-                              int dtype, int* status, cudaStream_t stream) {
+                              int dtype, int* status, cudaStream_t stream, const float* sink) {
     if (tokens == 0) return 0;
     if (latent < 1 || latent > lb::kLatentThreads * lb::kLatentMaxDimsPerThread || rope < 0) return -2;
     lb::LatentLayout layout{page_size, num_pages, max_blocks, latent, rope};
@@ -650,7 +674,7 @@ int lb_latent_attention_plain(const void* q, const void* pages, void* out, const
     LB_DISPATCH_DTYPE(dtype, {
         lb::latent_attention_plain_kernel<T><<<grid, lb::kLatentThreads, shared, stream>>>(
             static_cast<const T*>(q), static_cast<const T*>(pages), static_cast<T*>(out), positions, token_segment, block_table, layout, num_heads, scale,
-            window, status);
+            window, status, sink);
     })
     return LB_LAUNCH_RESULT();
 }
@@ -661,7 +685,7 @@ int lb_latent_attention_plain(const void* q, const void* pages, void* out, const
 int lb_latent_attention_mma(const void* q, const void* pages, void* out, float* partial, const int* items, int num_items, const int* positions,
                             const int* token_segment, const int* block_table, int tokens, int num_heads, int latent, int rope, int page_size,
                             int num_pages, int max_blocks, float scale, int window, int heads_per_cta, int tokens_per_cta, int splits, int* status,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, const float* sink) {
     if (num_items == 0 || tokens == 0) return 0;
     if (latent < 16 || latent % 16 != 0 || rope % 16 != 0 || page_size % 16 != 0 || heads_per_cta < 1 || tokens_per_cta < 1 ||
         heads_per_cta * tokens_per_cta > lb::kLatentMmaRows || splits < 1 || (splits > 1 && partial == nullptr))
@@ -692,6 +716,7 @@ int lb_latent_attention_mma(const void* q, const void* pages, void* out, float* 
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
+    p.sink = sink;
     const int chunk = wide ? 256 : 128;
     const dim3 grid(num_items, p.head_blocks * splits, (latent + chunk - 1) / chunk);
     if (wide) {
@@ -699,7 +724,7 @@ int lb_latent_attention_mma(const void* q, const void* pages, void* out, float* 
     } else {
         lb::latent_attention_mma_kernel<128><<<grid, lb::kLatentMmaThreads, shared, stream>>>(p);
     }
-    if (splits > 1) lb::latent_merge_kernel<<<tokens * num_heads, 128, splits * sizeof(float), stream>>>(partial, static_cast<__nv_bfloat16*>(out), splits, latent);
+    if (splits > 1) lb::latent_merge_kernel<<<tokens * num_heads, 128, splits * sizeof(float), stream>>>(partial, static_cast<__nv_bfloat16*>(out), splits, latent, sink, num_heads);
     return LB_LAUNCH_RESULT();
 }
 

@@ -46,6 +46,16 @@ __device__ __forceinline__ T* value_column(T* pages, const int* block_table, con
     return pages + base + (position - block * layout.page_size);
 }
 
+// What a projection-wide norm, scaled rotations and wider input rows add to the rewrite kernels below.
+struct RewriteExtras {
+    // [tokens][2] or null: rsqrt(mean(x^2) + eps) over all query columns and over all key columns of a token's row.
+    // Given, it replaces the per-head statistic; the weights then have one element per column of the projection
+    // (q_weight [heads * head_dim], k_weight [groups * head_dim]) and the norm is 32-bit with no rounding before the rotation.
+    const float* row_inv;
+    float turn_scale;   // sines and cosines are multiplied by this
+    int row_stride;     // elements between the rows of qkv (>= the q, k and v columns; what follows them is not read)
+};
+
 // grid (tokens, num_heads + num_groups), one warp per head vector.
 //   y < num_heads: query head -> q_out[token, head, :]
 //   else: key head g -> K page row (norm + rope), and value head g copied to the V page row.
@@ -58,7 +68,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
                                           const float* __restrict__ inv_freq, int rotary_dim,
                                           const int* __restrict__ positions, const int* __restrict__ token_segment,
                                           const int* __restrict__ block_table, PagedLayout layout, int num_heads,
-                                          int write_kv, const float* __restrict__ bias, int* status) {
+                                          int write_kv, const float* __restrict__ bias, int* status, RewriteExtras extra) {
     // Launched to start early; once the kernel before it (the q/k/v product) is done, the attention after it
     // may start in turn and read the keys and values that this kernel does not write.
     wait_for_previous_kernel();
@@ -67,13 +77,15 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
     const int unit = blockIdx.y;
     const int lane = threadIdx.x;
     const int hd = layout.head_dim, vd = layout.value_dim;
-    const int width = (num_heads + layout.num_groups) * hd + layout.num_groups * vd;
+    const int width = extra.row_stride;
     const bool is_query = unit < num_heads;
     if (!is_query && !write_kv) return;
     const int group = unit - num_heads;
     const T* src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(unit) * hd;
     const float* src_bias = bias ? bias + static_cast<size_t>(unit) * hd : nullptr;   // added in 32-bit, before the norm
     const float* weight = is_query ? q_weight : k_weight;
+    const bool whole = extra.row_inv != nullptr && weight != nullptr;
+    if (whole) weight += static_cast<size_t>(is_query ? unit : group) * hd;
     const int position = positions[token];
 
     T* dst;
@@ -94,7 +106,9 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
     }
 
     float inv = 1.0f;
-    if (weight != nullptr) {
+    if (whole) {
+        inv = extra.row_inv[2 * static_cast<size_t>(token) + (is_query ? 0 : 1)];
+    } else if (weight != nullptr) {
         float sum = 0.0f;
         for (int d = lane; d < hd; d += 32) {
             const float v = to_float(src[d]) + (src_bias ? src_bias[d] : 0.0f);
@@ -106,16 +120,18 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
     const int half = rotary_dim / 2;
     for (int d = lane; d < hd; d += 32) {
         float y = to_float(src[d]) + (src_bias ? src_bias[d] : 0.0f);
-        if (weight != nullptr) y = round_to<T>(round_to<T>(y * inv) * round_to<T>(weight[d] + scale_offset));
+        if (whole) y = y * inv * (weight[d] + scale_offset);
+        else if (weight != nullptr) y = round_to<T>(round_to<T>(y * inv) * round_to<T>(weight[d] + scale_offset));
         if (d < rotary_dim) {
             const int partner = d < half ? d + half : d - half;
             float other = to_float(src[partner]) + (src_bias ? src_bias[partner] : 0.0f);
-            if (weight != nullptr) other = round_to<T>(round_to<T>(other * inv) * round_to<T>(weight[partner] + scale_offset));
+            if (whole) other = other * inv * (weight[partner] + scale_offset);
+            else if (weight != nullptr) other = round_to<T>(round_to<T>(other * inv) * round_to<T>(weight[partner] + scale_offset));
             const float angle = static_cast<float>(position) * inv_freq[d < half ? d : d - half];
             float sine, cosine;
             sincosf(angle, &sine, &cosine);
             const float rotated = d < half ? -other : other;
-            y = y * cosine + rotated * sine;
+            y = (y * cosine + rotated * sine) * extra.turn_scale;
         }
         dst[d] = from_float<T>(y);
     }
@@ -133,20 +149,20 @@ __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __
                                                 const float* __restrict__ inv_freq, int rotary_dim,
                                                 const int* __restrict__ positions, const int* __restrict__ token_segment,
                                                 const int* __restrict__ block_table, PagedLayout layout, int num_heads,
-                                                int write_kv, const float* __restrict__ bias, int* status) {
+                                                int write_kv, const float* __restrict__ bias, int* status, RewriteExtras extra) {
     extern __shared__ float rotation[];   // cos[half], sin[half]
     const int token = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int hd = layout.head_dim, vd = layout.value_dim;
     const int half = rotary_dim / 2;
-    const int width = (num_heads + layout.num_groups) * hd + layout.num_groups * vd;
+    const int width = extra.row_stride;
     const int position = positions[token];
     const int segment = token_segment[token];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float sine, cosine;
         sincosf(static_cast<float>(position) * inv_freq[i], &sine, &cosine);
-        rotation[i] = cosine;
-        rotation[half + i] = sine;
+        rotation[i] = cosine * extra.turn_scale;
+        rotation[half + i] = sine * extra.turn_scale;
     }
     __syncthreads();
     const int units = num_heads + (write_kv ? layout.num_groups : 0);
@@ -158,6 +174,8 @@ __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __
         const T* src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(unit) * hd;
         const float* src_bias = bias ? bias + static_cast<size_t>(unit) * hd : nullptr;
         const float* weight = is_query ? q_weight : k_weight;
+        const bool whole = extra.row_inv != nullptr && weight != nullptr;
+        if (whole) weight += static_cast<size_t>(is_query ? unit : group) * hd;
         T* dst;
         if (is_query) {
             dst = q_out + (static_cast<size_t>(token) * num_heads + unit) * hd;
@@ -174,7 +192,9 @@ __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __
                 v_dst[static_cast<size_t>(d) * layout.page_size] = bias ? from_float<T>(to_float(v_src[d]) + bias[v_offset + d]) : v_src[d];
         }
         float inv = 1.0f;
-        if (weight != nullptr) {
+        if (whole) {
+            inv = extra.row_inv[2 * static_cast<size_t>(token) + (is_query ? 0 : 1)];
+        } else if (weight != nullptr) {
             float sum = 0.0f;
             for (int d = lane; d < hd; d += 32) {
                 const float v = to_float(src[d]) + (src_bias ? src_bias[d] : 0.0f);
@@ -185,11 +205,13 @@ __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __
         }
         for (int d = lane; d < hd; d += 32) {
             float y = to_float(src[d]) + (src_bias ? src_bias[d] : 0.0f);
-            if (weight != nullptr) y = round_to<T>(round_to<T>(y * inv) * round_to<T>(weight[d] + scale_offset));
+            if (whole) y = y * inv * (weight[d] + scale_offset);
+            else if (weight != nullptr) y = round_to<T>(round_to<T>(y * inv) * round_to<T>(weight[d] + scale_offset));
             if (d < rotary_dim) {
                 const int partner = d < half ? d + half : d - half;
                 float other = to_float(src[partner]) + (src_bias ? src_bias[partner] : 0.0f);
-                if (weight != nullptr) other = round_to<T>(round_to<T>(other * inv) * round_to<T>(weight[partner] + scale_offset));
+                if (whole) other = other * inv * (weight[partner] + scale_offset);
+                else if (weight != nullptr) other = round_to<T>(round_to<T>(other * inv) * round_to<T>(weight[partner] + scale_offset));
                 const int i = d < half ? d : d - half;
                 const float rotated = d < half ? -other : other;
                 y = y * rotation[i] + rotated * rotation[half + i];
@@ -221,19 +243,19 @@ __global__ void qk_norm_rope_write_vector_kernel(const __nv_bfloat16* __restrict
                                                  float scale_offset, const float* __restrict__ inv_freq, int rotary_dim,
                                                  const int* __restrict__ positions, const int* __restrict__ token_segment,
                                                  const int* __restrict__ block_table, PagedLayout layout, int num_heads, int write_kv,
-                                                 const float* __restrict__ bias, int* status) {
+                                                 const float* __restrict__ bias, int* status, RewriteExtras extra) {
     using T = __nv_bfloat16;
     extern __shared__ float rotation[];   // cos[half], sin[half]
     const int token = blockIdx.x;
     const int hd = layout.head_dim, lanes_per_head = hd / 8;
     const int half = rotary_dim / 2;
-    const int width = (num_heads + 2 * layout.num_groups) * hd;
+    const int width = extra.row_stride;
     const int position = positions[token];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float sine, cosine;
         sincosf(static_cast<float>(position) * inv_freq[i], &sine, &cosine);
-        rotation[i] = cosine;
-        rotation[half + i] = sine;
+        rotation[i] = cosine * extra.turn_scale;
+        rotation[half + i] = sine * extra.turn_scale;
     }
     __syncthreads();
     const int units = num_heads + (write_kv ? layout.num_groups : 0);
@@ -266,7 +288,13 @@ __global__ void qk_norm_rope_write_vector_kernel(const __nv_bfloat16* __restrict
         for (int i = 0; i < 8; ++i) sum += own[i] * own[i];
         for (int offset = 1; offset < lanes_per_head; offset <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
         const float inv = rsqrtf(sum / static_cast<float>(hd) + eps);
-        if (active && weight != nullptr) {
+        if (active && weight != nullptr && extra.row_inv != nullptr) {
+            // a norm over the whole projection: the token's statistic was computed before, the weights are the projection's
+            const float whole_inv = extra.row_inv[2 * static_cast<size_t>(token) + (is_query ? 0 : 1)];
+            const float* w = weight + static_cast<size_t>(is_query ? unit : group) * hd + chunk * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) own[i] = own[i] * whole_inv * (w[i] + scale_offset);
+        } else if (active && weight != nullptr) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) own[i] = round_to<T>(round_to<T>(own[i] * inv) * round_to<T>(weight[chunk * 8 + i] + scale_offset));
         }
@@ -323,7 +351,7 @@ __global__ void qk_norm_rope_write_run_kernel(const __nv_bfloat16* __restrict__ 
                                               float scale_offset, const float* __restrict__ inv_freq, int rotary_dim,
                                               const int* __restrict__ positions, const int* __restrict__ token_segment,
                                               const int* __restrict__ block_table, PagedLayout layout, int num_heads, int write_kv,
-                                              int tokens, const float* __restrict__ bias, int* status) {
+                                              int tokens, const float* __restrict__ bias, int* status, RewriteExtras extra) {
     static_assert(RUN == 4 || RUN == 8, "a channel's rows leave as one 8- or 16-byte store");
     using T = __nv_bfloat16;
     extern __shared__ float rotation[];   // per token of the run: cos[half], sin[half]
@@ -331,7 +359,7 @@ __global__ void qk_norm_rope_write_run_kernel(const __nv_bfloat16* __restrict__ 
     const int count = min(RUN, tokens - first);
     const int hd = layout.head_dim, lanes_per_head = hd / 8;
     const int half = rotary_dim / 2;
-    const int width = (num_heads + 2 * layout.num_groups) * hd;
+    const int width = extra.row_stride;
     const int units = num_heads + (write_kv ? layout.num_groups : 0);
     const int unit = threadIdx.x / lanes_per_head, chunk = threadIdx.x - unit * lanes_per_head;
     const bool active = unit < units;   // idle threads still take part in the shuffles
@@ -363,12 +391,17 @@ __global__ void qk_norm_rope_write_run_kernel(const __nv_bfloat16* __restrict__ 
         const int t = i / half, f = i - t * half;
         float sine, cosine;
         sincosf(static_cast<float>(positions[first + t]) * inv_freq[f], &sine, &cosine);
-        rotation[t * rotary_dim + f] = cosine;
-        rotation[t * rotary_dim + half + f] = sine;
+        rotation[t * rotary_dim + f] = cosine * extra.turn_scale;
+        rotation[t * rotary_dim + half + f] = sine * extra.turn_scale;
     }
+    const bool whole = extra.row_inv != nullptr && weight != nullptr;   // a norm over the whole projection, see RewriteExtras
     float scale[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) scale[i] = active && weight != nullptr ? round_to<T>(weight[chunk * 8 + i] + scale_offset) : 1.0f;
+    for (int i = 0; i < 8; ++i) {
+        scale[i] = 1.0f;
+        if (active && whole) scale[i] = weight[static_cast<size_t>(is_query ? unit : group) * hd + chunk * 8 + i] + scale_offset;
+        else if (active && weight != nullptr) scale[i] = round_to<T>(weight[chunk * 8 + i] + scale_offset);
+    }
     const int segment = token_segment[first];
     const int position0 = positions[first];
     // the run's values share their rows' 16-byte piece of each channel
@@ -393,7 +426,11 @@ __global__ void qk_norm_rope_write_run_kernel(const __nv_bfloat16* __restrict__ 
         for (int i = 0; i < 8; ++i) sum += own[i] * own[i];
         for (int offset = 1; offset < lanes_per_head; offset <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
         const float inv = rsqrtf(sum / static_cast<float>(hd) + eps);
-        if (active && weight != nullptr) {
+        if (active && whole && t < count) {
+            const float whole_inv = extra.row_inv[2 * static_cast<size_t>(first + t) + (is_query ? 0 : 1)];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) own[i] = own[i] * whole_inv * scale[i];
+        } else if (active && weight != nullptr) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) own[i] = round_to<T>(round_to<T>(own[i] * inv) * scale[i]);
         }
@@ -459,6 +496,21 @@ __global__ void qk_norm_rope_write_run_kernel(const __nv_bfloat16* __restrict__ 
             }
         }
     }
+}
+
+// grid (tokens, 2), one warp: inv[token][0] = rsqrt(mean over the q columns of x^2 + eps), inv[token][1] the same over the k columns.
+template <typename T>
+__global__ void projection_inv_rms_kernel(const T* __restrict__ qkv, int row_stride, int q_columns, int k_columns, float eps, float* __restrict__ inv) {
+    const int token = blockIdx.x, which = blockIdx.y;
+    const int columns = which == 0 ? q_columns : k_columns;
+    const T* src = qkv + static_cast<size_t>(token) * row_stride + (which == 0 ? 0 : q_columns);
+    float sum = 0.0f;
+    for (int d = threadIdx.x; d < columns; d += 32) {
+        const float v = to_float(src[d]);
+        sum += v * v;
+    }
+    sum = warp_sum(sum);
+    if (threadIdx.x == 0) inv[2 * static_cast<size_t>(token) + which] = rsqrtf(sum / static_cast<float>(columns) + eps);
 }
 
 constexpr int kRunKernelMinTokens = 512;   // below, a block per token fills the GPU better
@@ -562,15 +614,29 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
                           const float* k_weight, float eps, float scale_offset, const float* inv_freq, int rotary_dim,
                           const int* positions, const int* token_segment, const int* block_table, int tokens,
                           int num_heads, int num_groups, int head_dim, int page_size, int num_pages, int max_blocks,
-                          int write_kv, int dtype, int* status, cudaStream_t stream, int value_dim, const float* bias) {
+                          int write_kv, int dtype, int* status, cudaStream_t stream, int value_dim, const float* bias, float* row_inv,
+                          float turn_scale, int row_stride) {
+    // row_inv: scratch [tokens][2] for a norm over the whole q and the whole k projection (null: the norm is per head);
+    // turn_scale: a factor on sines and cosines; row_stride: elements between qkv's rows (0: the q, k and v columns).
     if (tokens == 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2 != 0) return -2;
     if (value_dim <= 0) value_dim = head_dim;
+    const int columns = (num_heads + num_groups) * head_dim + num_groups * value_dim;
+    if (row_stride <= 0) row_stride = columns;
+    if (row_stride < columns || (row_inv != nullptr && (q_weight == nullptr || bias != nullptr))) return -2;
+    const lb::RewriteExtras extra{row_inv, turn_scale, row_stride};
+    if (row_inv != nullptr) {
+        LB_DISPATCH_DTYPE(dtype, {
+            lb::projection_inv_rms_kernel<T><<<dim3(tokens, 2), 32, 0, stream>>>(static_cast<const T*>(qkv), row_stride, num_heads * head_dim,
+                                                                                 num_groups * head_dim, eps, row_inv);
+        })
+    }
     lb::PagedLayout layout{page_size, num_pages, max_blocks, num_groups, head_dim, value_dim};
     const bool plain_layout = value_dim == head_dim;   // what the 16-byte kernels below take
     const bool power_of_two_head = head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128;
     const int vector_threads = (((num_heads + num_groups) * (head_dim / 8)) + 31) / 32 * 32;
     if (tokens > 64 && plain_layout && dtype == lb::kBFloat16 && power_of_two_head && rotary_dim % 16 == 0 && rotary_dim <= head_dim && vector_threads <= 1024 &&
+        row_stride % 8 == 0 &&
         ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0) {
         const size_t shared = static_cast<size_t>(rotary_dim > 0 ? rotary_dim : 2) * sizeof(float);
         if (tokens >= lb::kRunKernelMinTokens) {
@@ -578,13 +644,13 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
             lb::qk_norm_rope_write_run_kernel<kRun><<<(tokens + kRun - 1) / kRun, vector_threads, kRun * shared, stream>>>(
                 static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_pages),
                 static_cast<__nv_bfloat16*>(v_pages), q_weight, k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table,
-                layout, num_heads, write_kv, tokens, bias, status);
+                layout, num_heads, write_kv, tokens, bias, status, extra);
             return LB_LAUNCH_RESULT();
         }
         lb::qk_norm_rope_write_vector_kernel<<<tokens, vector_threads, shared, stream>>>(
             static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_pages),
             static_cast<__nv_bfloat16*>(v_pages), q_weight, k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table,
-            layout, num_heads, write_kv, bias, status);
+            layout, num_heads, write_kv, bias, status, extra);
         return LB_LAUNCH_RESULT();
     }
     if (tokens > 64) {
@@ -594,7 +660,7 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
             lb::qk_norm_rope_write_token_kernel<T><<<dim3(tokens, (num_heads + num_groups + lb::kTokenKernelUnits - 1) / lb::kTokenKernelUnits), 128, shared, stream>>>(
                 static_cast<const T*>(qkv), static_cast<T*>(q_out), static_cast<T*>(k_pages), static_cast<T*>(v_pages), q_weight,
                 k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table, layout, num_heads,
-                write_kv, bias, status);
+                write_kv, bias, status, extra);
         })
         return LB_LAUNCH_RESULT();
     }
@@ -603,7 +669,7 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
         lb::launch_overlapped(lb::qk_norm_rope_write_kernel<T>, grid, dim3(32), 0, stream,
             static_cast<const T*>(qkv), static_cast<T*>(q_out), static_cast<T*>(k_pages), static_cast<T*>(v_pages), q_weight,
             k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table, layout, num_heads,
-            write_kv, bias, status);
+            write_kv, bias, status, extra);
     })
     return LB_LAUNCH_RESULT();
 }

@@ -48,7 +48,11 @@ template <typename TX, typename T>
 __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials, int slices,
                                size_t slice_stride, const float* __restrict__ weight,
                                const int* __restrict__ rows, T* __restrict__ out, int dim, float eps,
-                               float scale_offset, int write_back, int exact) {
+                               float scale_offset, int write_back, int exact, const float* __restrict__ bias, int centred,
+                               const float* __restrict__ delta_bias) {
+    // bias (may be null): added to the output, out[r] = T(n * (w + offset) + bias).  centred: a layer norm,
+    // n = (h - mean(h)) * rsqrt(mean((h - mean(h))^2) + eps), 32-bit throughout (taken with `exact`).
+    // delta_bias (may be null; with a delta only): a 32-bit vector added to the delta, h = x + (delta + delta_bias).
     extern __shared__ float shared[];
     // Launched to start early: it is resident when the kernel before it ends (no launch in between).  Only then
     // may the product after it start and pull its weights towards L2: under the stream of the kernel before,
@@ -76,6 +80,13 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
                 h.y += low.y;
                 h.z += high.x;
                 h.w += high.y;
+            }
+            if (adds && delta_bias) {
+                const float4 b = *reinterpret_cast<const float4*>(delta_bias + d);
+                h.x += b.x;
+                h.y += b.y;
+                h.z += b.z;
+                h.w += b.w;
             }
             if (pr) {
                 // Four slices' loads leave before the first is added (the order of the additions stays).
@@ -112,6 +123,7 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
         for (int d = threadIdx.x; d < dim; d += blockDim.x) {
             float h = to_float(xr[d]);
             if (dr) h += to_float(dr[d]);
+            if (adds && delta_bias) h += delta_bias[d];
             if (pr) {
                 float total = 0.0f;
                 for (int s = 0; s < slices; ++s) total += pr[static_cast<size_t>(s) * slice_stride + d];
@@ -121,14 +133,61 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
             sum += h * h;
         }
     }
+    T* dst = out + static_cast<size_t>(r) * dim;
+    if (centred) {
+        // the mean first, then the squared deviations from it (each thread rereads what it wrote)
+        float plain = 0.0f;
+        if (kVector && dim % 4 == 0) {
+            for (int d = 4 * threadIdx.x; d < dim; d += 4 * blockDim.x) plain += (row_cache[d] + row_cache[d + 1]) + (row_cache[d + 2] + row_cache[d + 3]);
+        } else {
+            for (int d = threadIdx.x; d < dim; d += blockDim.x) plain += row_cache[d];
+        }
+        const float mean = block_sum(plain, scratch) / static_cast<float>(dim);
+        float squares = 0.0f;
+        if (kVector && dim % 4 == 0) {
+            for (int d = 4 * threadIdx.x; d < dim; d += 4 * blockDim.x) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float c = row_cache[d + e] - mean;
+                    squares += c * c;
+                }
+            }
+        } else {
+            for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+                const float c = row_cache[d] - mean;
+                squares += c * c;
+            }
+        }
+        const float inv_dev = rsqrtf(block_sum(squares, scratch) / static_cast<float>(dim) + eps);
+        if (kVector && dim % 4 == 0) {
+            for (int d = 4 * threadIdx.x; d < dim; d += 4 * blockDim.x) {
+                const float4 h = *reinterpret_cast<const float4*>(row_cache + d);
+                if (write_back && adds) *reinterpret_cast<float4*>(reinterpret_cast<float*>(xr) + d) = h;
+                const float4 w = *reinterpret_cast<const float4*>(weight + d);
+                const float4 b = bias ? *reinterpret_cast<const float4*>(bias + d) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                const __nv_bfloat162 low = __floats2bfloat162_rn((h.x - mean) * inv_dev * (w.x + scale_offset) + b.x, (h.y - mean) * inv_dev * (w.y + scale_offset) + b.y);
+                const __nv_bfloat162 high = __floats2bfloat162_rn((h.z - mean) * inv_dev * (w.z + scale_offset) + b.z, (h.w - mean) * inv_dev * (w.w + scale_offset) + b.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<const uint32_t*>(&low);
+                packed.y = *reinterpret_cast<const uint32_t*>(&high);
+                *reinterpret_cast<uint2*>(dst + d) = packed;
+            }
+        } else {
+            for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+                const float h = row_cache[d];
+                if (write_back && adds) xr[d] = from_float<TX>(h);
+                dst[d] = from_float<T>((h - mean) * inv_dev * (weight[d] + scale_offset) + (bias ? bias[d] : 0.0f));
+            }
+        }
+        return;
+    }
     const float total = block_sum(sum, scratch);
     const float inv = rsqrtf(total / static_cast<float>(dim) + eps);
-    T* dst = out + static_cast<size_t>(r) * dim;
     if (exact) {
         for (int d = threadIdx.x; d < dim; d += blockDim.x) {
             const float h = row_cache[d];
             if (write_back && adds) xr[d] = from_float<TX>(h);
-            dst[d] = from_float<T>(h * inv * (weight[d] + scale_offset));
+            dst[d] = from_float<T>(h * inv * (weight[d] + scale_offset) + (bias ? bias[d] : 0.0f));
         }
     } else if (kVector && dim % 4 == 0) {
         for (int d = 4 * threadIdx.x; d < dim; d += 4 * blockDim.x) {
@@ -329,10 +388,41 @@ __global__ void norm_accumulate_kernel(float* __restrict__ residual, const T* __
     for (int d = threadIdx.x; d < dim; d += blockDim.x) rounded[base + d] = from_float<T>(row_cache[d] * next_inv * (next_weight[d] + next_offset));
 }
 
-// x[i] *= factor (32-bit, in place)
-__global__ void scale_kernel(float* __restrict__ x, float factor, size_t count) {
+// x[i] *= factor (32-bit, in place); with cap > 0 then x[i] = cap * tanh(x[i] / cap)
+__global__ void scale_kernel(float* __restrict__ x, float factor, size_t count, float cap) {
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i < count) x[i] *= factor;
+    if (i >= count) return;
+    const float v = x[i] * factor;
+    x[i] = cap > 0.0f ? cap * tanhf(v / cap) : v;
+}
+
+// out[r, d] = T(act(x[r, d] + bias[d])) with the activation codes of the products' epilogues (bias may be null)
+template <typename T>
+__global__ void bias_activation_kernel(const T* __restrict__ x, const float* __restrict__ bias, T* __restrict__ out, int dim, size_t count, int activation) {
+    allow_next_kernel();
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = from_float<T>(activate(to_float(x[i]) + (bias ? bias[i % dim] : 0.0f), activation));
+}
+
+// out[t] = [T(stream[t]) | T(float(table[ids[t]]) * scale)]: the residual stream and the embedding's output side by
+// side, rounded to the activation type, as the input of a projection that renews the stream from both.
+template <typename T>
+__global__ void stream_concat_kernel(const float* __restrict__ stream, const T* __restrict__ table, const int* __restrict__ ids, T* __restrict__ out,
+                                     int dim, int vocab, float scale, int* status) {
+    allow_next_kernel();
+    const int token = blockIdx.x;
+    int id = ids[token];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) report_error(status, kBadToken);
+        id = 0;
+    }
+    const float* src = stream + static_cast<size_t>(token) * dim;
+    const T* row = table + static_cast<size_t>(id) * dim;
+    T* dst = out + static_cast<size_t>(token) * 2 * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        dst[d] = from_float<T>(src[d]);
+        dst[dim + d] = from_float<T>(to_float(row[d]) * scale);
+    }
 }
 
 }  // namespace lb
@@ -369,8 +459,9 @@ int lb_embed(const void* table, const int* ids, float* out, int tokens, int dim,
 // partials, slices, slice_stride: see rmsnorm_kernel (slices == 0: none); the vector path needs slice_stride % 4 == 0.
 int lb_rmsnorm(void* x, int x_is_float, const void* delta, const float* partials, int slices, long long slice_stride, const float* weight,
                const int* rows, void* out, int out_rows, int dim, float eps, float scale_offset, int write_back, int dtype, cudaStream_t stream,
-               int exact) {
+               int exact, const float* bias, int centred, const float* delta_bias) {
     if (out_rows == 0) return 0;
+    if ((bias != nullptr || centred) && !exact) return -2;   // an output bias and the layer norm exist in the 32-bit form only
     if (slices < 0 || (slices > 0 && (partials == nullptr || slice_stride < 0 || (dim % 4 == 0 && slice_stride % 4 != 0)))) return -2;
     const size_t shared = (static_cast<size_t>(dim) + 33) * sizeof(float);
     if (shared > 200 * 1024) return -2;
@@ -386,12 +477,12 @@ int lb_rmsnorm(void* x, int x_is_float, const void* delta, const float* partials
             auto kernel = lb::rmsnorm_kernel<float, T>;
             if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
             lb::launch_overlapped(kernel, dim3(out_rows), dim3(threads), shared, stream, static_cast<float*>(x), static_cast<const T*>(delta), partials, slices,
-                                  static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back, exact);
+                                  static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back, exact, bias, centred, delta_bias);
         } else {
             auto kernel = lb::rmsnorm_kernel<T, T>;
             if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
             lb::launch_overlapped(kernel, dim3(out_rows), dim3(threads), shared, stream, static_cast<T*>(x), static_cast<const T*>(delta), partials, slices,
-                                  static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back, exact);
+                                  static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back, exact, bias, centred, delta_bias);
         }
     })
     return LB_LAUNCH_RESULT();
@@ -479,9 +570,29 @@ int lb_norm_accumulate(float* residual, const void* a, const float* bias_a, floa
     return LB_LAUNCH_RESULT();
 }
 
-int lb_scale(float* x, float factor, long long count, cudaStream_t stream) {
+int lb_scale(float* x, float factor, long long count, cudaStream_t stream, float cap) {
     if (count == 0) return 0;
-    lb::scale_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(x, factor, static_cast<size_t>(count));
+    lb::scale_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(x, factor, static_cast<size_t>(count), cap);
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_bias_activation(const void* x, const float* bias, void* out, int rows, int dim, int activation, int dtype, cudaStream_t stream) {
+    const size_t count = static_cast<size_t>(rows) * dim;
+    if (count == 0) return 0;
+    if (activation < 0 || activation > 2) return -2;
+    const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::bias_activation_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T*>(x), bias, static_cast<T*>(out), dim, count, activation);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_stream_concat(const float* stream_rows, const void* table, const int* ids, void* out, int tokens, int dim, int vocab, float scale, int dtype,
+                     int* status, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::stream_concat_kernel<T><<<tokens, 256, 0, stream>>>(stream_rows, static_cast<const T*>(table), ids, static_cast<T*>(out), dim, vocab, scale, status);
+    })
     return LB_LAUNCH_RESULT();
 }
 

@@ -53,7 +53,9 @@ __global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, c
                                    float* __restrict__ beta_out, float* __restrict__ g_out,
                                    const int* __restrict__ token_segment, const int* __restrict__ segment_start,
                                    const int* __restrict__ segment_slot, int heads, int groups, int dk, int dv, int taps,
-                                   int num_slots, float unit_eps, float q_scale, int* status) {
+                                   int num_slots, float unit_eps, float q_scale, int* status, int decay_per_head) {
+    // decay_per_head: `ag` holds one decay logit per head (heads columns) and dt_bias one element per head; the head's
+    // decay is written to all of its key channels.
     // UPDATE: every portion of the step is one token, and the lane that convolves a channel (the only reader of that
     // channel's rows in the slot) also shifts the rows and appends the token's input; no state kernel runs after this one.
     // (Otherwise the state is read-only here, and says so: the loads were a third slower without it.)
@@ -116,7 +118,12 @@ __global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, c
             const float rate = expf(a_log[head]);
             const T* a_row = ag + static_cast<size_t>(token) * ag_width + static_cast<size_t>(head) * dk;
             float* dst = g_out + (static_cast<size_t>(token) * heads + head) * dk;
-            for (int c = lane; c < dk; c += 32) dst[c] = expf(-rate * softplusf_(to_float(a_row[c]) + dt_bias[head * dk + c]));
+            if (decay_per_head) {
+                const float decay = expf(-rate * softplusf_(to_float(ag[static_cast<size_t>(token) * ag_width + head]) + dt_bias[head]));
+                for (int c = lane; c < dk; c += 32) dst[c] = decay;
+            } else {
+                for (int c = lane; c < dk; c += 32) dst[c] = expf(-rate * softplusf_(to_float(a_row[c]) + dt_bias[head * dk + c]));
+            }
             if (lane == 0) beta_out[static_cast<size_t>(token) * heads + head] = sigmoidf_(to_float(proj[static_cast<size_t>(token) * proj_width + channels + head]));
         }
     }
@@ -335,7 +342,7 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
 // grid (tokens, slices of the heads), a warp per head: out[t, h, :] = T(o / sqrt(mean(o^2) + eps) * w * sigmoid(gate[t, h, :])).
 template <typename T>
 __global__ void gdr_output_kernel(const float* __restrict__ o, const T* __restrict__ ag, int ag_width, int gate_offset,
-                                  const float* __restrict__ norm_weight, T* __restrict__ out, int heads, int dv, float eps) {
+                                  const float* __restrict__ norm_weight, T* __restrict__ out, int heads, int dv, float eps, int gate_silu) {
     allow_next_kernel();   // the out-projection, launched to start early, may ask for its weights meanwhile
     const int token = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
@@ -347,7 +354,10 @@ __global__ void gdr_output_kernel(const float* __restrict__ o, const T* __restri
         sum = warp_sum(sum);
         const float inv = rsqrtf(sum / static_cast<float>(dv) + eps);
         T* dst = out + (static_cast<size_t>(token) * heads + head) * dv;
-        for (int c = lane; c < dv; c += 32) dst[c] = from_float<T>(row[c] * inv * norm_weight[c] * sigmoidf_(to_float(gate[c])));
+        for (int c = lane; c < dv; c += 32) {
+            const float z = to_float(gate[c]);
+            dst[c] = from_float<T>(row[c] * inv * norm_weight[c] * (gate_silu ? z * sigmoidf_(z) : sigmoidf_(z)));
+        }
     }
 }
 
@@ -494,7 +504,8 @@ extern "C" {
 int lb_gdr_prepare(const void* proj, int proj_width, const void* ag, int ag_width, void* conv_state, const float* conv_weight,
                    const float* a_log, const float* dt_bias, float* q_out, float* k_out, float* v_out, float* beta_out, float* g_out,
                    const int* token_segment, const int* segment_start, const int* segment_slot, int tokens, int heads, int groups, int dk,
-                   int dv, int taps, int num_slots, float unit_eps, float q_scale, int dtype, int* status, cudaStream_t stream, int update_state) {
+                   int dv, int taps, int num_slots, float unit_eps, float q_scale, int dtype, int* status, cudaStream_t stream, int update_state,
+                   int decay_per_head) {
     if (tokens == 0) return 0;
     if (dk > 32 * lb::kPrepareMaxPerLane || taps < 1 || heads % groups != 0) return -2;
     LB_DISPATCH_DTYPE(dtype, {
@@ -504,12 +515,12 @@ int lb_gdr_prepare(const void* proj, int proj_width, const void* ag, int ag_widt
             lb::gdr_prepare_kernel<T, true><<<grid, 128, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<const T*>(ag), ag_width,
                                                                        static_cast<T*>(conv_state), conv_weight, a_log, dt_bias, q_out, k_out, v_out, beta_out, g_out,
                                                                        token_segment, segment_start, segment_slot, heads, groups, dk, dv, taps, num_slots, unit_eps,
-                                                                       q_scale, status);
+                                                                       q_scale, status, decay_per_head);
         else
             lb::gdr_prepare_kernel<T, false><<<grid, 128, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<const T*>(ag), ag_width,
                                                                         static_cast<const T*>(conv_state), conv_weight, a_log, dt_bias, q_out, k_out, v_out, beta_out,
                                                                         g_out, token_segment, segment_start, segment_slot, heads, groups, dk, dv, taps, num_slots,
-                                                                        unit_eps, q_scale, status);
+                                                                        unit_eps, q_scale, status, decay_per_head);
     })
     return LB_LAUNCH_RESULT();
 }
@@ -573,10 +584,10 @@ int lb_gdr_chunk_finish(const float* chunk_state, float* chunk_in, float* state,
 }
 
 int lb_gdr_output(const float* o, const void* ag, int ag_width, int gate_offset, const float* norm_weight, void* out, int tokens, int heads, int dv,
-                  float eps, int dtype, cudaStream_t stream) {
+                  float eps, int dtype, cudaStream_t stream, int gate_silu) {
     if (tokens == 0) return 0;
     LB_DISPATCH_DTYPE(dtype, {
-        lb::gdr_output_kernel<T><<<dim3(tokens, (heads + 3) / 4), 128, 0, stream>>>(o, static_cast<const T*>(ag), ag_width, gate_offset, norm_weight, static_cast<T*>(out), heads, dv, eps);
+        lb::gdr_output_kernel<T><<<dim3(tokens, (heads + 3) / 4), 128, 0, stream>>>(o, static_cast<const T*>(ag), ag_width, gate_offset, norm_weight, static_cast<T*>(out), heads, dv, eps, gate_silu);
     })
     return LB_LAUNCH_RESULT();
 }

@@ -43,6 +43,7 @@ struct SkinnyParams {
     int segments, taps, num_slots;
     int* status;
     int prefetch;   // ask for the CTA's rows of W towards L2 before waiting for the kernel before this one
+    const float* bias;   // [n] or null: added to the sums of the store and residual-add epilogues (the store then applies `activation`)
 };
 
 __device__ __forceinline__ void mma_16816_skinny(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -170,9 +171,12 @@ gemm_skinny_kernel(const SkinnyParams p) {
             const int row = index % ROWS, token = index / ROWS;
             if (token >= p.tokens) continue;
             const size_t where = static_cast<size_t>(token) * p.n + row0 + row;
-            const float value = total[0][row][token];
+            float value = total[0][row][token];
+            if constexpr (EPILOGUE == kStore || EPILOGUE == kStoreFloat || EPILOGUE == kResidualAdd) {
+                if (p.bias != nullptr) value += p.bias[row0 + row];
+            }
             if constexpr (EPILOGUE == kStore) {
-                static_cast<__nv_bfloat16*>(p.out)[where] = __float2bfloat16_rn(value);
+                static_cast<__nv_bfloat16*>(p.out)[where] = __float2bfloat16_rn(skinny_activate(value, p.activation));
             } else if constexpr (EPILOGUE == kStoreFloat) {
                 static_cast<float*>(p.out)[where] = value;
             } else if constexpr (EPILOGUE == kResidualAdd) {
@@ -259,7 +263,7 @@ extern "C" {
 int lb_gemm_skinny(const void* x, const void* w, void* out, int tokens, int k, int n, int epilogue, int activation,
                    void* state, const float* conv_weight, const float* conv_bias, const int* token_segment,
                    const int* segment_start, const int* segment_length, const int* segment_slot, int segments, int taps,
-                   int num_slots, int prefetch, int* status, cudaStream_t stream, float limit) {
+                   int num_slots, int prefetch, int* status, cudaStream_t stream, float limit, const float* bias) {
     if (tokens == 0) return 0;
     if (tokens < 1 || tokens > 16 || k % 32 != 0 || n % 8 != 0 || k < 32) return -2;
     lb::SkinnyParams p;
@@ -283,6 +287,7 @@ int lb_gemm_skinny(const void* x, const void* w, void* out, int tokens, int k, i
     p.taps = taps;
     p.num_slots = num_slots;
     p.status = status;
+    p.bias = bias;
     p.prefetch = prefetch && (reinterpret_cast<uintptr_t>(w) & 15) == 0 ? 1 : 0;
     switch (epilogue) {
         case lb::kStore: return lb::launch_skinny<1, lb::kStore>(p, stream);

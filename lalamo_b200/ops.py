@@ -19,7 +19,7 @@ import torch
 
 from . import native
 
-__all__ = ["ExpertSum", "KernelError", "ScaledSum", "SlicedSum", "dtype_code", "launch_count", "reset_launch_count"]
+__all__ = ["BiasedSum", "ExpertSum", "KernelError", "ScaledSum", "SlicedSum", "dtype_code", "launch_count", "reset_launch_count"]
 
 
 class KernelError(RuntimeError):
@@ -44,6 +44,25 @@ class SlicedSum:
         slices, tokens, rows = self.partials.shape
         out = torch.empty(tokens, rows, dtype=self.dtype, device=self.partials.device)
         _sum_slices(self.partials, out, "store")
+        return out
+
+
+@dataclass
+class BiasedSum:
+    """A product ``tensor`` (or a :class:`SlicedSum`) whose bias, a 32-bit vector over its columns, is still to be added:
+    :func:`rmsnorm` adds both to the residual stream on its way, :func:`residual_add` likewise; :meth:`sum` gives the
+    plain tensor."""
+
+    tensor: "torch.Tensor | SlicedSum"
+    bias: torch.Tensor
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.tensor.shape
+
+    def sum(self) -> torch.Tensor:
+        out = self.tensor.sum() if isinstance(self.tensor, SlicedSum) else self.tensor.clone()
+        add_bias(out, self.bias)
         return out
 
 
@@ -187,14 +206,19 @@ def rmsnorm(
     out: torch.Tensor,
     eps: float,
     *,
-    delta: torch.Tensor | SlicedSum | None = None,
+    delta: "torch.Tensor | SlicedSum | BiasedSum | None" = None,
     rows: torch.Tensor | None = None,
     scale_offset: float = 0.0,
     write_back: bool = False,
     exact: bool = False,
+    bias: torch.Tensor | None = None,
+    centred: bool = False,
 ) -> None:
     """``out[r] = rms_norm(x[src] + delta[src]) * (weight + offset)``, ``src = rows[r]`` or ``r``.
     ``exact``: 32-bit throughout and rounded once (otherwise the normalised value and the scale are each rounded first).
+    ``bias`` (32-bit, with ``exact``) is added to the output; ``centred`` (with ``exact``) makes it a layer norm,
+    ``(h - mean) * rsqrt(mean((h - mean)^2) + eps) * (weight + offset) + bias``.  ``delta`` may carry a bias of its own
+    (:class:`BiasedSum`), added to the stream with it.
 
     ``x`` is the 32-bit residual stream or has ``out``'s type.  With ``write_back`` the sum is
     stored back into ``x``.  ``delta`` may be a :class:`SlicedSum`: its slices are added here.
@@ -209,6 +233,18 @@ def rmsnorm(
     if x.dtype != torch.float32 and x.dtype != out.dtype:
         raise KernelError("rmsnorm: x must be float32 or of out's type")
     partials, slices, slice_stride = None, 0, 0
+    delta_bias = None
+    if isinstance(delta, BiasedSum):
+        delta, delta_bias = delta.tensor, delta.bias
+        _check(delta_bias, "delta bias", torch.float32)
+        if delta_bias.numel() != dim:
+            raise KernelError("rmsnorm: the delta's bias must have one element per column")
+    if (bias is not None or centred) and not exact:
+        raise KernelError("rmsnorm: an output bias and the layer norm exist in the exact (32-bit) form only")
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.numel() != dim:
+            raise KernelError("rmsnorm: bias must have one element per column")
     if isinstance(delta, SlicedSum):
         _check(delta.partials, "delta.partials", torch.float32)
         if delta.shape != x.shape or delta.dtype != out.dtype:
@@ -229,7 +265,8 @@ def rmsnorm(
         raise KernelError(f"rmsnorm: rows of {dim} elements exceed the supported 50000")
     code = _lib().lb_rmsnorm(_ptr(x), c_int(1 if x.dtype == torch.float32 else 0),
                              _ptr(delta), _ptr(partials), c_int(slices), c_longlong(slice_stride), _ptr(weight), _ptr(rows), _ptr(out), c_int(out_rows), c_int(dim), c_float(eps),
-                             c_float(scale_offset), c_int(1 if write_back else 0), c_int(dtype_code(out.dtype)), _stream(), c_int(1 if exact else 0))
+                             c_float(scale_offset), c_int(1 if write_back else 0), c_int(dtype_code(out.dtype)), _stream(), c_int(1 if exact else 0),
+                             _ptr(bias), c_int(1 if centred else 0), _ptr(delta_bias))
     _done(code, "rmsnorm")
 
 
@@ -245,6 +282,8 @@ def _sum_slices(partials: torch.Tensor, out: torch.Tensor, epilogue: str) -> Non
 def residual_add(x: torch.Tensor, delta: torch.Tensor | SlicedSum) -> None:
     """``x += delta`` on the 32-bit residual stream (a :class:`SlicedSum` is summed and rounded first)."""
     _check(x, "x", torch.float32)
+    if isinstance(delta, BiasedSum):
+        delta = delta.sum()
     if isinstance(delta, SlicedSum):
         if delta.dtype != torch.bfloat16:
             raise KernelError("residual_add: a sliced sum is rounded to bfloat16")
@@ -328,10 +367,44 @@ def norm_accumulate(residual: torch.Tensor, delta: "torch.Tensor | ScaledSum", w
     _done(code, "norm_accumulate")
 
 
-def scale_(x: torch.Tensor, factor: float) -> None:
-    """``x *= factor`` in place on a 32-bit tensor."""
+def scale_(x: torch.Tensor, factor: float, softcap: float = 0.0) -> None:
+    """``x *= factor`` in place on a 32-bit tensor; with ``softcap`` > 0 then ``x = softcap * tanh(x / softcap)``."""
     _check(x, "x", torch.float32)
-    _done(_lib().lb_scale(_ptr(x), c_float(factor), c_longlong(x.numel()), _stream()), "scale")
+    if softcap < 0.0:
+        raise KernelError("scale_: the cap must not be negative")
+    _done(_lib().lb_scale(_ptr(x), c_float(factor), c_longlong(x.numel()), _stream(), c_float(softcap)), "scale")
+
+
+def bias_activation(x: torch.Tensor, bias: torch.Tensor | None, activation: str) -> torch.Tensor:
+    """``act(x + bias)`` (32-bit arithmetic, rounded once to ``x``'s type); ``activation``: ``"silu"``, ``"gelu"`` (exact) or ``"identity"``."""
+    _check(x, "x")
+    if activation not in ("silu", "gelu", "identity"):
+        raise KernelError(f"bias_activation: unknown activation {activation!r}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if x.dim() != 2 or bias.numel() != x.shape[1]:
+            raise KernelError("bias_activation: bias must have one element per column of x")
+    out = torch.empty_like(x)
+    code = _lib().lb_bias_activation(_ptr(x), _ptr(bias), _ptr(out), c_int(x.shape[0]), c_int(x.shape[1]), c_int(_ACTIVATIONS[activation]),
+                                     c_int(dtype_code(x.dtype)), _stream())
+    _done(code, "bias_activation")
+    return out
+
+
+def stream_concat(stream: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float, status: torch.Tensor) -> torch.Tensor:
+    """``[stream[t] | float(table[ids[t]]) * scale]`` per token, rounded to the table's type: the 32-bit residual stream and
+    the embedding's output side by side, ``[tokens, 2 * dim]``."""
+    _check(stream, "stream", torch.float32)
+    _check(table, "table")
+    _check(ids, "ids", torch.int32)
+    tokens, dim = stream.shape
+    if table.shape[1] != dim or ids.numel() < tokens:
+        raise KernelError("stream_concat: shapes of stream, table and ids do not agree")
+    out = torch.empty(tokens, 2 * dim, dtype=table.dtype, device=stream.device)
+    code = _lib().lb_stream_concat(_ptr(stream), _ptr(table), _ptr(ids), _ptr(out), c_int(tokens), c_int(dim), c_int(table.shape[0]), c_float(scale),
+                                   c_int(dtype_code(table.dtype)), _ptr(status), _stream())
+    _done(code, "stream_concat")
+    return out
 
 
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
@@ -425,17 +498,25 @@ def qk_norm_rope_write(
     status: torch.Tensor,
     value_dim: int | None = None,
     bias: torch.Tensor | None = None,
+    whole_norm: bool = False,
+    turn_scale: float = 1.0,
 ) -> None:
     """Splits ``qkv`` rows into heads, applies per-head norm and rotary embedding to queries and
     keys, writes queries to ``q_out`` and keys/values into their pages.  ``value_dim``: the size of a
     value head where it differs from ``head_dim``; ``bias``: a 32-bit vector over ``qkv``'s columns,
-    added before the norm."""
-    _check(qkv, "qkv")
+    added before the norm.  ``whole_norm``: the norm runs over all of a token's query columns at once (and
+    over all of its key columns), with weights of one element per column, in 32-bit with no rounding before the
+    rotation.  ``turn_scale`` multiplies sines and cosines.  ``qkv`` may be the first columns of a wider product."""
+    if not qkv.is_cuda or qkv.dim() != 2 or qkv.stride(1) != 1:
+        raise KernelError("qk_norm_rope_write: qkv must be a [tokens, .] CUDA tensor with unit column stride")
     _check(q_out, "q_out", qkv.dtype)
     tokens = qkv.shape[0]
     value_dim = value_dim or head_dim
     if qkv.shape[1] != (num_heads + num_groups) * head_dim + num_groups * value_dim or q_out.numel() != tokens * num_heads * head_dim:
         raise KernelError("qk_norm_rope_write: qkv / q_out widths do not match the head counts")
+    if whole_norm and (q_weight is None or bias is not None):
+        raise KernelError("qk_norm_rope_write: a norm over the whole projection needs weights and takes no bias")
+    row_inv = torch.empty(tokens, 2, dtype=torch.float32, device=qkv.device) if whole_norm else None
     if bias is not None:
         _check(bias, "bias", torch.float32)
         if bias.numel() != qkv.shape[1]:
@@ -448,8 +529,8 @@ def qk_norm_rope_write(
     for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
         if weight is not None:
             _check(weight, name, torch.float32)
-            if weight.numel() != head_dim:
-                raise KernelError(f"{name} must have head_dim elements")
+            if weight.numel() != (head_dim if not whole_norm else head_dim * (num_heads if name == "q_weight" else num_groups)):
+                raise KernelError(f"{name} must have head_dim elements (one per column of the projection for a norm over the whole of it)")
     if rotary_dim:
         if inv_freq is None:
             raise KernelError("qk_norm_rope_write: rotary_dim > 0 needs inv_freq")
@@ -462,8 +543,8 @@ def qk_norm_rope_write(
         _ptr(qkv), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(q_weight), _ptr(k_weight), c_float(eps), c_float(scale_offset),
         _ptr(inv_freq), c_int(rotary_dim), _ptr(positions), _ptr(token_segment), _ptr(block_table), c_int(tokens), c_int(num_heads),
         c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks), c_int(1 if write_kv else 0),
-        c_int(dtype_code(qkv.dtype)), _ptr(status), _stream(), c_int(value_dim), _ptr(bias))
-    _done(code, "qk_norm_rope_write")
+        c_int(dtype_code(qkv.dtype)), _ptr(status), _stream(), c_int(value_dim), _ptr(bias), _ptr(row_inv), c_float(turn_scale), c_int(qkv.stride(0)))
+    _done(code, "qk_norm_rope_write", 2 if whole_norm else 1)
 
 
 def paged_attention_plain(
@@ -810,6 +891,9 @@ def gated_delta_rule(
     segments: int,
     status: torch.Tensor,
     chunk_plan: dict | None = None,
+    decay_per_head: bool = False,
+    gate_activation: str = "sigmoid",
+    gate_offset: int | None = None,
 ) -> torch.Tensor:
     """The gated delta rule with a decay per head and key channel over the step's portions, from each
     request's state slot and back into it.  ``chunk_plan`` (see :func:`gated_delta_chunk_plan`; int32 arrays on
@@ -822,9 +906,17 @@ def gated_delta_rule(
     logits.  ``conv_weight`` is ``[C, taps]`` (last column: the current token), ``conv_state``
     ``[slots, taps - 1, C]`` (the convolutions' last inputs, in the activation type), ``matrix_state``
     ``[slots, heads, key_dim, value_dim]`` in 32-bit.  Returns the gated, normed read-out
-    ``[tokens, heads * value_dim]`` in the activation type."""
+    ``[tokens, heads * value_dim]`` in the activation type.
+
+    ``decay_per_head``: one decay per head; ``low_rank`` then begins with ``heads`` decay logits and ``dt_bias`` has ``heads``
+    elements.  ``gate_offset``: the column of ``low_rank`` at which the gate's logits begin (default: right after the decay
+    logits).  ``gate_activation``: ``"sigmoid"`` or ``"silu"``.  ``low_rank`` may be a column slice of a wider product
+    (of ``proj`` itself, for instance)."""
     _check(proj, "proj")
-    _check(low_rank, "low_rank", proj.dtype)
+    if not low_rank.is_cuda or low_rank.dim() != 2 or low_rank.stride(1) != 1 or low_rank.dtype != proj.dtype:
+        raise KernelError("gated_delta_rule: low_rank must be a [tokens, .] CUDA tensor of proj's type with unit column stride")
+    if gate_activation not in ("sigmoid", "silu"):
+        raise KernelError(f"gated_delta_rule: unknown gate activation {gate_activation!r}")
     _check(matrix_state, "matrix_state", torch.float32)
     for name, tensor in (("conv_weight", conv_weight), ("a_log", a_log), ("dt_bias", dt_bias), ("norm_weight", norm_weight)):
         _check(tensor, name, torch.float32)
@@ -835,9 +927,11 @@ def gated_delta_rule(
     taps = conv_weight.shape[1]
     if num_heads % num_groups or key_dim < 1 or key_dim > 256 or value_dim < 1:
         raise KernelError(f"gated_delta_rule: {num_heads} heads over {num_groups} groups with key size {key_dim} (at most 256) is not supported")
-    if proj.shape[1] < channels + num_heads or low_rank.shape != (tokens, num_heads * (key_dim + value_dim)):
+    decay_columns = num_heads if decay_per_head else num_heads * key_dim
+    gate_offset = decay_columns if gate_offset is None else gate_offset
+    if proj.shape[1] < channels + num_heads or low_rank.shape[0] != tokens or gate_offset < decay_columns or low_rank.shape[1] < gate_offset + num_heads * value_dim:
         raise KernelError("gated_delta_rule: proj or low_rank is too narrow for the head counts")
-    if conv_weight.shape != (channels, taps) or a_log.numel() != num_heads or dt_bias.numel() != num_heads * key_dim or norm_weight.numel() != value_dim:
+    if conv_weight.shape != (channels, taps) or a_log.numel() != num_heads or dt_bias.numel() != decay_columns or norm_weight.numel() != value_dim:
         raise KernelError("gated_delta_rule: conv_weight, a_log, dt_bias or norm_weight has the wrong size")
     num_slots = matrix_state.shape[0]
     if matrix_state.shape != (num_slots, num_heads, key_dim, value_dim):
@@ -856,10 +950,11 @@ def gated_delta_rule(
     decay = torch.empty(tokens, num_heads, key_dim, dtype=torch.float32, device=device)
     lib = _lib()
     single_tokens = segments == tokens   # every portion is one token: the convolutions' kernel also writes their new state
-    code = lib.lb_gdr_prepare(_ptr(proj), c_int(proj.shape[1]), _ptr(low_rank), c_int(low_rank.shape[1]), _ptr(conv_state), _ptr(conv_weight), _ptr(a_log),
+    code = lib.lb_gdr_prepare(_ptr(proj), c_int(proj.shape[1]), _ptr(low_rank), c_int(low_rank.stride(0)), _ptr(conv_state), _ptr(conv_weight), _ptr(a_log),
                               _ptr(dt_bias), _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(token_segment), _ptr(segment_start), _ptr(segment_slot),
                               c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(key_dim), c_int(value_dim), c_int(taps), c_int(num_slots),
-                              c_float(unit_eps), c_float(key_dim ** -0.5), c_int(dtype_code(proj.dtype)), _ptr(status), _stream(), c_int(1 if single_tokens else 0))
+                              c_float(unit_eps), c_float(key_dim ** -0.5), c_int(dtype_code(proj.dtype)), _ptr(status), _stream(), c_int(1 if single_tokens else 0),
+                              c_int(1 if decay_per_head else 0))
     _done(code, "gdr_prepare")
     if taps > 1 and not single_tokens:
         code = lib.lb_gdr_conv_state(_ptr(proj), c_int(proj.shape[1]), _ptr(conv_state), _ptr(segment_start), _ptr(segment_length), _ptr(segment_slot),
@@ -894,8 +989,8 @@ def gated_delta_rule(
                                _ptr(status), _stream(), _ptr(direct_list), c_int(value_dim))
         _done(code, "gdr_scan")
     out = torch.empty(tokens, num_heads * value_dim, dtype=proj.dtype, device=device)
-    code = lib.lb_gdr_output(_ptr(read_out), _ptr(low_rank), c_int(low_rank.shape[1]), c_int(num_heads * key_dim), _ptr(norm_weight), _ptr(out), c_int(tokens),
-                             c_int(num_heads), c_int(value_dim), c_float(norm_eps), c_int(dtype_code(proj.dtype)), _stream())
+    code = lib.lb_gdr_output(_ptr(read_out), _ptr(low_rank), c_int(low_rank.stride(0)), c_int(gate_offset), _ptr(norm_weight), _ptr(out), c_int(tokens),
+                             c_int(num_heads), c_int(value_dim), c_float(norm_eps), c_int(dtype_code(proj.dtype)), _stream(), c_int(1 if gate_activation == "silu" else 0))
     _done(code, "gdr_output")
     return out
 
@@ -975,11 +1070,20 @@ def latent_prepare(q: torch.Tensor, q_latent: torch.Tensor | None, down: torch.T
     _done(code, "latent_prepare")
 
 
+def _check_sink(sink: torch.Tensor | None, num_heads: int) -> None:
+    if sink is not None:
+        _check(sink, "sink", torch.float32)
+        if sink.numel() != num_heads:
+            raise KernelError("latent attention: the sink must have one number per head")
+
+
 def latent_attention_plain(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, *, positions: torch.Tensor, token_segment: torch.Tensor,
                            block_table: torch.Tensor, num_heads: int, latent: int, rope: int, scale: float, window: int | None,
-                           status: torch.Tensor) -> None:
+                           status: torch.Tensor, sink: torch.Tensor | None = None) -> None:
     """Causal (optionally windowed) attention of queries ``[tokens, heads, latent + rope]`` over their requests' cached rows
-    ``[latent | rope]``: ``out[t, h] = sum_j softmax_j(q[t, h] . row_j * scale) row_j[:latent]``, all in 32-bit."""
+    ``[latent | rope]``: ``out[t, h] = sum_j softmax_j(q[t, h] . row_j * scale) row_j[:latent]``, all in 32-bit.  ``sink``
+    (32-bit, one number per head): ``exp(sink[h])`` joins the softmax's denominator, unscaled and with no row behind it."""
+    _check_sink(sink, num_heads)
     _check(q, "q")
     _check(out, "out", q.dtype)
     tokens = q.shape[0]
@@ -992,7 +1096,7 @@ def latent_attention_plain(q: torch.Tensor, pages: torch.Tensor, out: torch.Tens
         raise KernelError(f"latent_attention: latent {latent} + rope {rope} exceed what the kernel supports")
     code = _lib().lb_latent_attention_plain(_ptr(q), _ptr(pages), _ptr(out), _ptr(positions), _ptr(token_segment), _ptr(block_table), c_int(tokens),
                                             c_int(num_heads), c_int(latent), c_int(rope), c_int(page_size), c_int(num_pages), c_int(max_blocks),
-                                            c_float(scale), c_int(window if window else 0), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
+                                            c_float(scale), c_int(window if window else 0), c_int(dtype_code(q.dtype)), _ptr(status), _stream(), _ptr(sink))
     _done(code, "latent_attention_plain")
 
 
@@ -1024,10 +1128,12 @@ def latent_attention_splits(num_items: int, num_heads: int, latent: int, window:
 
 def latent_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, *, items: torch.Tensor, num_items: int, positions: torch.Tensor,
                      token_segment: torch.Tensor, block_table: torch.Tensor, num_heads: int, latent: int, rope: int, scale: float, window: int | None,
-                     status: torch.Tensor, splits: int = 1) -> None:
+                     status: torch.Tensor, splits: int = 1, sink: torch.Tensor | None = None) -> None:
     """:func:`latent_attention_plain` on the tensor cores (bfloat16).  ``items``: int32 ``[num_items, 2]`` (first token row,
     count), each at most ``latent_attention_tiling(num_heads)[1]`` consecutive tokens of one request, together all tokens.
-    ``splits`` > 1 shares an item's cached rows out over that many CTAs, merged in split order."""
+    ``splits`` > 1 shares an item's cached rows out over that many CTAs, merged in split order.  ``sink``: as for
+    :func:`latent_attention_plain`."""
+    _check_sink(sink, num_heads)
     _check(q, "q", torch.bfloat16)
     _check(out, "out", torch.bfloat16)
     _check(items, "items", torch.int32)
@@ -1042,7 +1148,7 @@ def latent_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, *,
     code = _lib().lb_latent_attention_mma(_ptr(q), _ptr(pages), _ptr(out), _ptr(partial), _ptr(items), c_int(num_items), _ptr(positions), _ptr(token_segment),
                                           _ptr(block_table), c_int(tokens), c_int(num_heads), c_int(latent), c_int(rope), c_int(page_size), c_int(num_pages),
                                           c_int(max_blocks), c_float(scale), c_int(window if window else 0), c_int(heads_per_cta), c_int(tokens_per_cta),
-                                          c_int(splits), _ptr(status), _stream())
+                                          c_int(splits), _ptr(status), _stream(), _ptr(sink))
     _done(code, "latent_attention_mma", 2 if splits > 1 else 1)
 
 
@@ -1245,7 +1351,7 @@ def skinny_supported(x: torch.Tensor, rows: int) -> bool:
 
 
 def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, epilogue: str, activation: str = "identity", conv: dict | None = None,
-            prefetch: bool = True, limit: float = 0.0) -> None:
+            prefetch: bool = True, limit: float = 0.0, bias: torch.Tensor | None = None) -> None:
     """``prefetch``: the kernel asks for its weights towards L2 before it waits for the kernel before it; off where
     that kernel does not let it start early (see :func:`successor_starts_early`)."""
     conv = conv or {}
@@ -1253,7 +1359,8 @@ def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, ep
         _ptr(x), _ptr(weight), _ptr(out), c_int(x.shape[0]), c_int(x.shape[1]), c_int(n), c_int(_SKINNY_EPILOGUES[epilogue]),
         c_int(_ACTIVATIONS[activation]), _ptr(conv.get("state")), _ptr(conv.get("weight")), _ptr(conv.get("bias")), _ptr(conv.get("token_segment")),
         _ptr(conv.get("segment_start")), _ptr(conv.get("segment_length")), _ptr(conv.get("segment_slot")), c_int(conv.get("segments", 0)),
-        c_int(conv.get("taps", 0)), c_int(conv.get("num_slots", 0)), c_int(1 if prefetch else 0), _ptr(conv.get("status")), _stream(), c_float(limit))
+        c_int(conv.get("taps", 0)), c_int(conv.get("num_slots", 0)), c_int(1 if prefetch else 0), _ptr(conv.get("status")), _stream(), c_float(limit),
+        _ptr(bias))
     _done(code, f"gemm_skinny[{epilogue}]")
 
 
@@ -1393,6 +1500,30 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     return torch.mm(x, weight.t())
 
 
+def linear_bias_activation(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, activation: str,
+                           status: torch.Tensor | None = None) -> torch.Tensor:
+    """``act(x @ weight.T + bias)`` in ``x``'s type (the sum and the activation in 32-bit, rounded once).  Steps of up to 16
+    tokens compute it in the weight-streaming product's epilogue; other steps run the product, then one elementwise kernel."""
+    _check(x, "x")
+    _check(weight, "weight", x.dtype)
+    if activation not in ("silu", "gelu", "identity"):
+        raise KernelError(f"linear_bias_activation: unknown activation {activation!r}")
+    if x.shape[-1] != weight.shape[1]:
+        raise KernelError(f"linear_bias_activation: input width {x.shape[-1]} does not match the weight's {weight.shape[1]}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.numel() != weight.shape[0]:
+            raise KernelError("linear_bias_activation: bias must have one element per row of the weight")
+    if skinny_supported(x, weight.shape[0]):
+        out = torch.empty(x.shape[0], weight.shape[0], dtype=x.dtype, device=x.device)
+        _skinny(x, weight, out, weight.shape[0], "store", activation, bias=bias)
+        return out
+    product = linear(x, weight, status=status)
+    if isinstance(product, SlicedSum):
+        product = product.sum()
+    return bias_activation(product, bias, activation)
+
+
 def gated_linear_starts_successor_early(tokens: int, rows: int, width: int) -> bool:
     """Whether the kernel :func:`gated_linear` runs for these sizes lets the kernel after it start before it has
     finished (the weight-streaming kernel does; the TMA kernel only with more than 16 tokens): a successor that
@@ -1402,11 +1533,24 @@ def gated_linear_starts_successor_early(tokens: int, rows: int, width: int) -> b
 
 
 def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, status: torch.Tensor | None = None,
-                      started_early: bool = True) -> torch.Tensor | SlicedSum | None:
+                      started_early: bool = True, bias: torch.Tensor | None = None) -> "torch.Tensor | SlicedSum | BiasedSum | None":
     """``residual += x @ weight.T`` (the product rounded to the activation type first) when the fused
     kernel takes the product: returns ``None``.  Otherwise returns the product, not yet added: a tensor,
     or a :class:`SlicedSum` when the product was cut into K slices (the norm that follows adds them).
-    ``started_early=False``: the kernel before this one does not let its successor start early."""
+    ``started_early=False``: the kernel before this one does not let its successor start early.
+    ``bias`` (32-bit, one element per row of the weight) is added with the product: in the fused kernel's epilogue,
+    or by whoever adds what is returned (a :class:`BiasedSum`)."""
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.numel() != weight.shape[0]:
+            raise KernelError("linear_accumulate: bias must have one element per row of the weight")
+        if skinny_supported(x, weight.shape[0]) and x.shape[-1] == weight.shape[1] and residual.shape == (x.shape[0], weight.shape[0]):
+            _check(x, "x")
+            _check(weight, "weight", x.dtype)
+            _check(residual, "residual", torch.float32)
+            _skinny(x, weight, residual, weight.shape[0], "residual_add", prefetch=started_early, bias=bias)
+            return None
+        return BiasedSum(linear(x, weight, status=status), bias)
     _check(x, "x")
     _check(weight, "weight", x.dtype)
     _check(residual, "residual", torch.float32)

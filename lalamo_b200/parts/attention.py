@@ -84,14 +84,16 @@ class Attention(Mixer):
             # reordering of the channels of q and k changes none of them: the even channels of the rotated part first,
             # then the odd ones, and pair (2i, 2i + 1) becomes pair (i, i + rotary_dim / 2) with its angle.
             if spec.qk_norm is not None:
-                raise ValueError("interleaved rotation with a per-head norm is not supported (the norm's weight would have to be reordered too)")
+                raise ValueError("interleaved rotation with a norm of q and k is not supported (the norm's weight would have to be reordered too)")
             order = _interleaved_to_half(spec.head_dim, spec.position.rotary_dim)
             q_proj, k_proj = _reorder_heads(q_proj, spec.num_heads, order), _reorder_heads(k_proj, spec.num_groups, order)
             if spec.has_bias:
                 q_bias, k_bias = _reorder_heads(q_bias, spec.num_heads, order), _reorder_heads(k_bias, spec.num_groups, order)
         elif isinstance(spec.position, RopeSpec) and spec.position.pairing != "half":
             raise ValueError(f"unknown rotary pairing {spec.position.pairing!r}; known: 'half', 'interleaved'")
-        self.qkv = runtime.matrix(torch.cat([q_proj, k_proj, tensors["v_proj"]], dim=0))
+        # One product for everything that reads the mixer's input: queries, keys, values and, behind them, the gate's logits.
+        self.qkv_width = q_proj.shape[0] + k_proj.shape[0] + tensors["v_proj"].shape[0]
+        self.qkv = runtime.matrix(torch.cat([q_proj, k_proj, tensors["v_proj"]] + ([tensors["gate_proj"]] if spec.gated else []), dim=0))
         self.out_proj = runtime.matrix(tensors["out_proj"])
         # Biases are 32-bit vectors: those of q, k and v are added where the product's rows are split into heads,
         # the output's by whoever consumes the output (`output_bias`), or here.
@@ -102,6 +104,8 @@ class Attention(Mixer):
         if spec.qk_norm is not None:
             if not isinstance(spec.qk_norm, RMSNormSpec) or spec.qk_norm.dim != spec.head_dim:
                 raise ValueError("the per-head norm must be an RMS norm over head_dim")
+            if spec.qk_norm_whole and spec.has_bias:
+                raise ValueError("a norm over the whole projection with biases on q and k is not supported")
             self.q_norm = runtime.vector(tensors["q_norm"])
             self.k_norm = runtime.vector(tensors["k_norm"])
             self.norm_eps, self.norm_offset = spec.qk_norm.eps, spec.qk_norm.scale_offset
@@ -126,8 +130,11 @@ class Attention(Mixer):
             decls["v_bias"] = TensorDecl((spec.num_groups * (spec.value_dim or spec.head_dim),), role="vector")
             decls["out_bias"] = TensorDecl((spec.model_dim,), role="vector")
         if spec.qk_norm is not None:
-            decls["q_norm"] = TensorDecl((spec.head_dim,), role="vector", init="ones")
-            decls["k_norm"] = TensorDecl((spec.head_dim,), role="vector", init="ones")
+            # per head, or one element per row of the projection where the norm runs over the whole of it
+            decls["q_norm"] = TensorDecl((spec.head_dim * (spec.num_heads if spec.qk_norm_whole else 1),), role="vector", init="ones")
+            decls["k_norm"] = TensorDecl((spec.head_dim * (spec.num_groups if spec.qk_norm_whole else 1),), role="vector", init="ones")
+        if spec.gated:
+            decls["gate_proj"] = TensorDecl((spec.num_heads * (spec.value_dim or spec.head_dim), spec.model_dim))
         return decls
 
     def cache_need(self) -> CacheNeed | None:
@@ -154,7 +161,12 @@ class Attention(Mixer):
 
     can_accumulate = True
 
-    def _project_out(self, mixed: torch.Tensor, residual: torch.Tensor | None, add_output_bias: bool = True) -> torch.Tensor | None:
+    def _project_out(self, mixed: torch.Tensor, residual: torch.Tensor | None, add_output_bias: bool = True, gate: torch.Tensor | None = None) -> torch.Tensor | None:
+        if gate is not None:
+            # the concatenated heads times sigmoid(gate), the gate's logits being the last columns of the in-projection
+            gated = self.runtime.empty(*mixed.shape)
+            ops.gate_heads(mixed.view(1, *mixed.shape), gate, gated)
+            mixed = gated
         if self.output_bias is not None:
             out = ops.linear(mixed, self.out_proj, status=self.runtime.status)
             if isinstance(out, ops.SlicedSum):
@@ -170,7 +182,9 @@ class Attention(Mixer):
                 add_output_bias: bool = True) -> torch.Tensor | None:
         """``add_output_bias=False``: the caller adds :attr:`output_bias` to what this returns."""
         spec = self.spec
-        qkv = ops.linear(x, self.qkv, status=self.runtime.status)
+        projected = ops.linear(x, self.qkv, status=self.runtime.status)
+        qkv = projected[:, : self.qkv_width] if spec.gated else projected
+        gate = projected[:, self.qkv_width :] if spec.gated else None
         queries = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
         ops.qk_norm_rope_write(
             qkv,
@@ -193,6 +207,8 @@ class Attention(Mixer):
             status=self.runtime.status,
             value_dim=self.value_dim,
             bias=self.qkv_bias,
+            whole_norm=spec.qk_norm_whole and spec.qk_norm is not None,
+            turn_scale=self.position.magnitude if self.position is not None else 1.0,
         )
         mixed = self.runtime.empty(step.tokens, spec.num_heads * self.value_dim)
         page_size = cache.k_pages.shape[1]
@@ -230,7 +246,7 @@ class Attention(Mixer):
                     split_tiles = shared_tile_keys(num_tiles, spec.num_heads, spec.num_groups, ops.sm_count(), step.tokens,
                                                    step.host_segment_length, step.host_segment_context) // 64
                 ops.attention_prefill(queries, cache.k_pages, cache.v_pages, mixed, tiles=lists["tiles"], num_tiles=num_tiles, split_tiles=split_tiles, **common)
-            return self._project_out(mixed, residual, add_output_bias)
+            return self._project_out(mixed, residual, add_output_bias, gate)
         ops.paged_attention_plain(
             queries,
             cache.k_pages,
@@ -248,4 +264,4 @@ class Attention(Mixer):
             value_dim=self.value_dim,
             keep_first=self.keep_first,
         )
-        return self._project_out(mixed, residual, add_output_bias)
+        return self._project_out(mixed, residual, add_output_bias, gate)

@@ -90,8 +90,13 @@ class Block:
 class PreNormBlock(Block):
     roles = ("pre_mixer_norm", "mixer", "pre_ffn_norm", "ffn")
     pre_mixer_norm: Norm
-    pre_ffn_norm: Norm
-    ffn: FeedForward
+    pre_ffn_norm: Norm | None
+    ffn: FeedForward | None
+
+    def __init__(self, spec: Any, tensors: Mapping[tuple[str, str], torch.Tensor], runtime: Runtime) -> None:
+        super().__init__(spec, tensors, runtime)
+        if (self.ffn is None) != (self.pre_ffn_norm is None):
+            raise ValueError("a pre-norm block has a feed-forward with its norm, or neither")
 
     def forward(self, residual: torch.Tensor, pending: torch.Tensor | None, step: StepInputs, cache: CacheView | None) -> torch.Tensor | None:
         normed = self.pre_mixer_norm.residual_forward(residual, pending)
@@ -99,6 +104,8 @@ class PreNormBlock(Block):
             mixed = self.mixer.forward(normed, step, cache, residual=residual)
         else:
             mixed = self.mixer.forward(normed, step, cache)
+        if self.ffn is None:
+            return mixed   # the next block's norm (or the model's last) adds it
         normed = self.pre_ffn_norm.residual_forward(residual, mixed)
         if self.ffn.can_accumulate:
             return self.ffn.forward(normed, step, residual=residual)

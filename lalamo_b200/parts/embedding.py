@@ -11,10 +11,10 @@ from typing import Mapping
 import torch
 
 from .. import ops
-from ..config.plan import EmbeddingSpec, HeadSpec
+from ..config.plan import EmbeddingSpec, HeadSpec, StreamMixSpec
 from .base import Part, Runtime, TensorDecl, register_part
 
-__all__ = ["Embedding", "Head", "LMHead", "TokenEmbedding"]
+__all__ = ["Embedding", "Head", "LMHead", "StreamMix", "TokenEmbedding"]
 
 
 class Embedding(Part):
@@ -67,6 +67,26 @@ class LMHead(Head):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         logits = ops.linear(x, self.weight, out_dtype=torch.float32, status=self.runtime.status)
-        if self.spec.scale != 1.0:
-            ops.scale_(logits, self.spec.scale)
+        if self.spec.scale != 1.0 or self.spec.softcap > 0.0:
+            ops.scale_(logits, self.spec.scale, self.spec.softcap)
         return logits
+
+
+@register_part(StreamMixSpec)
+class StreamMix(Part):
+    """``x <- W [x ; x0]``: the residual stream renewed from itself and the embedding's output.  The two are laid side by side,
+    rounded to the activation type (the embedding's rows are gathered again, nothing is kept), and one product with 32-bit
+    results writes the new stream."""
+
+    def __init__(self, spec: StreamMixSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().__init__(spec, tensors, runtime)
+        self.weight = runtime.matrix(tensors["weight"])
+
+    @classmethod
+    def tensor_decls(cls, spec: StreamMixSpec) -> dict[str, TensorDecl]:
+        return {"weight": TensorDecl((spec.model_dim, 2 * spec.model_dim))}
+
+    def forward(self, residual: torch.Tensor, embedding: "TokenEmbedding", token_ids: torch.Tensor) -> torch.Tensor:
+        """The new 32-bit stream for the stream ``residual`` (everything added) and the tokens' embeddings."""
+        both = ops.stream_concat(residual, embedding.weight, token_ids, embedding.spec.scale, self.runtime.status)
+        return ops.linear(both, self.weight, out_dtype=torch.float32, status=self.runtime.status)

@@ -8,10 +8,10 @@ from typing import Mapping
 import torch
 
 from .. import ops
-from ..config.plan import GatedMLPSpec
+from ..config.plan import DenseMLPSpec, GatedMLPSpec
 from .base import FeedForward, Runtime, StepInputs, TensorDecl, register_part
 
-__all__ = ["GatedMLP"]
+__all__ = ["DenseMLP", "GatedMLP"]
 
 
 @register_part(GatedMLPSpec)
@@ -37,3 +37,41 @@ class GatedMLP(FeedForward):
             early = ops.gated_linear_starts_successor_early(x.shape[0], self.up_gate.shape[0], x.shape[1])
             return ops.linear_accumulate(hidden, self.down, residual, status=self.runtime.status, started_early=early)
         return ops.linear(hidden, self.down, status=self.runtime.status)
+
+
+@register_part(DenseMLPSpec)
+class DenseMLP(FeedForward):
+    """``down(act(up(x) + b_up)) + b_down``: two projections around an activation, no gate.  The up-projection's bias and the
+    activation are the product's epilogue for steps of few tokens (one elementwise kernel after the product otherwise); the
+    down-projection's bias is added with the product, onto the 32-bit stream, by whoever adds it."""
+
+    def __init__(self, spec: DenseMLPSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().__init__(spec, tensors, runtime)
+        self.up = runtime.matrix(tensors["up_proj"])
+        self.down = runtime.matrix(tensors["down_proj"])
+        self.up_bias = runtime.vector(tensors["up_bias"]) if spec.has_bias else None
+        self.down_bias = runtime.vector(tensors["down_bias"]) if spec.has_bias else None
+
+    @classmethod
+    def tensor_decls(cls, spec: DenseMLPSpec) -> dict[str, TensorDecl]:
+        decls = {
+            "up_proj": TensorDecl((spec.hidden_dim, spec.model_dim)),
+            "down_proj": TensorDecl((spec.model_dim, spec.hidden_dim)),
+        }
+        if spec.has_bias:
+            decls["up_bias"] = TensorDecl((spec.hidden_dim,), role="vector")
+            decls["down_bias"] = TensorDecl((spec.model_dim,), role="vector")
+        return decls
+
+    can_accumulate = True
+
+    def forward(self, x: torch.Tensor, step: StepInputs | None = None, residual: torch.Tensor | None = None):
+        hidden = ops.linear_bias_activation(x, self.up, self.up_bias, self.spec.activation, status=self.runtime.status)
+        if residual is not None:
+            return ops.linear_accumulate(hidden, self.down, residual, status=self.runtime.status, bias=self.down_bias)
+        out = ops.linear(hidden, self.down, status=self.runtime.status)
+        if isinstance(out, ops.SlicedSum):
+            out = out.sum()
+        if self.down_bias is not None:
+            ops.add_bias(out, self.down_bias)
+        return out

@@ -5,7 +5,9 @@ followed by a per-head RMS norm, a low-rank sigmoid gate and the out-projection.
 Three products feed the recurrence's kernels: ``[q ; k ; v ; beta]`` (rows padded to a multiple of 8),
 the two bottlenecks ``[a1 ; g1]`` (each padded to a multiple of 32 columns for the next product), and
 the block-diagonal ``[a2 0 ; 0 g2]`` that turns the bottlenecks into decay and gate logits; the padding
-is zeros and changes no sum.  Per request the mixer holds the matrix state in 32-bit and the
+is zeros and changes no sum.  Without bottlenecks (``decay_rank = gate_rank = 0``) the decay and gate logits are
+rows of the first product, ``[q ; k ; v ; beta ; a ; g]``, and that product is the only one.  The decay is one number
+per head and key channel, or one per head.  Per request the mixer holds the matrix state in 32-bit and the
 convolutions' last ``taps - 1`` inputs in the activation type."""
 
 from __future__ import annotations
@@ -34,23 +36,40 @@ class GatedDelta(Mixer):
         super().__init__(spec, tensors, runtime)
         if spec.num_heads % spec.num_groups:
             raise ValueError(f"num_heads={spec.num_heads} is not a multiple of num_groups={spec.num_groups}")
-        if spec.conv_taps < 1 or spec.decay_rank < 1 or spec.gate_rank < 1:
-            raise ValueError("conv_taps, decay_rank and gate_rank must be positive")
+        if spec.conv_taps < 1 or spec.decay_rank < 0 or spec.gate_rank < 0:
+            raise ValueError("conv_taps must be positive, decay_rank and gate_rank not negative")
+        if (spec.decay_rank == 0) != (spec.gate_rank == 0):
+            raise ValueError("the decay and the gate both go through a bottleneck, or neither does")
+        if spec.gate_activation not in ("sigmoid", "silu"):
+            raise ValueError(f"unknown gate activation {spec.gate_activation!r}; known: 'sigmoid', 'silu'")
         heads, groups, dk, dv = spec.num_heads, spec.num_groups, spec.key_dim, spec.value_dim
         self.channels = 2 * groups * dk + heads * dv
+        self.direct = spec.decay_rank == 0
+        decay_columns = heads * dk if spec.decay_per_channel else heads
         rows = torch.cat([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"], tensors["beta_proj"]], dim=0)
-        padded = torch.zeros(_round_up(rows.shape[0], 8), spec.model_dim, dtype=rows.dtype)
-        padded[: rows.shape[0]] = rows
-        self.in_proj = runtime.matrix(padded)
-        decay_rank, gate_rank = _round_up(spec.decay_rank, 32), _round_up(spec.gate_rank, 32)
-        down = torch.zeros(decay_rank + gate_rank, spec.model_dim, dtype=rows.dtype)
-        down[: spec.decay_rank] = tensors["decay_down"]
-        down[decay_rank : decay_rank + spec.gate_rank] = tensors["gate_down"]
-        self.low_rank_down = runtime.matrix(down)
-        up = torch.zeros(heads * dk + heads * dv, decay_rank + gate_rank, dtype=rows.dtype)
-        up[: heads * dk, : spec.decay_rank] = tensors["decay_up"]
-        up[heads * dk :, decay_rank : decay_rank + spec.gate_rank] = tensors["gate_up"]
-        self.low_rank_up = runtime.matrix(up)
+        if self.direct:
+            # [q ; k ; v ; beta | a | g], each part starting at a multiple of 8 rows
+            self.decay_offset = _round_up(rows.shape[0], 8)
+            self.gate_offset = _round_up(decay_columns, 8)   # counted from the decay logits
+            padded = torch.zeros(_round_up(self.decay_offset + self.gate_offset + heads * dv, 8), spec.model_dim, dtype=rows.dtype)
+            padded[: rows.shape[0]] = rows
+            padded[self.decay_offset : self.decay_offset + decay_columns] = tensors["decay_proj"]
+            padded[self.decay_offset + self.gate_offset : self.decay_offset + self.gate_offset + heads * dv] = tensors["gate_proj"]
+            self.in_proj = runtime.matrix(padded)
+        else:
+            self.gate_offset = decay_columns
+            padded = torch.zeros(_round_up(rows.shape[0], 8), spec.model_dim, dtype=rows.dtype)
+            padded[: rows.shape[0]] = rows
+            self.in_proj = runtime.matrix(padded)
+            decay_rank, gate_rank = _round_up(spec.decay_rank, 32), _round_up(spec.gate_rank, 32)
+            down = torch.zeros(decay_rank + gate_rank, spec.model_dim, dtype=rows.dtype)
+            down[: spec.decay_rank] = tensors["decay_down"]
+            down[decay_rank : decay_rank + spec.gate_rank] = tensors["gate_down"]
+            self.low_rank_down = runtime.matrix(down)
+            up = torch.zeros(decay_columns + heads * dv, decay_rank + gate_rank, dtype=rows.dtype)
+            up[:decay_columns, : spec.decay_rank] = tensors["decay_up"]
+            up[decay_columns:, decay_rank : decay_rank + spec.gate_rank] = tensors["gate_up"]
+            self.low_rank_up = runtime.matrix(up)
         self.conv_weight = runtime.vector(torch.cat([tensors["q_conv"], tensors["k_conv"], tensors["v_conv"]], dim=0).reshape(self.channels, spec.conv_taps))
         self.a_log = runtime.vector(tensors["a_log"])
         self.dt_bias = runtime.vector(tensors["dt_bias"])
@@ -60,6 +79,16 @@ class GatedDelta(Mixer):
     @classmethod
     def tensor_decls(cls, spec: GatedDeltaSpec) -> dict[str, TensorDecl]:
         heads, groups, dk, dv = spec.num_heads, spec.num_groups, spec.key_dim, spec.value_dim
+        decay_columns = heads * dk if spec.decay_per_channel else heads
+        if spec.decay_rank == 0:
+            logits = {"decay_proj": TensorDecl((decay_columns, spec.model_dim)), "gate_proj": TensorDecl((heads * dv, spec.model_dim))}
+        else:
+            logits = {
+                "decay_down": TensorDecl((spec.decay_rank, spec.model_dim)),
+                "decay_up": TensorDecl((decay_columns, spec.decay_rank)),
+                "gate_down": TensorDecl((spec.gate_rank, spec.model_dim)),
+                "gate_up": TensorDecl((heads * dv, spec.gate_rank)),
+            }
         return {
             "q_proj": TensorDecl((groups * dk, spec.model_dim)),
             "k_proj": TensorDecl((groups * dk, spec.model_dim)),
@@ -69,11 +98,8 @@ class GatedDelta(Mixer):
             "v_conv": TensorDecl((heads * dv, spec.conv_taps), role="vector"),
             "beta_proj": TensorDecl((heads, spec.model_dim)),
             "a_log": TensorDecl((heads,), role="vector", init="zeros"),
-            "dt_bias": TensorDecl((heads * dk,), role="vector"),
-            "decay_down": TensorDecl((spec.decay_rank, spec.model_dim)),
-            "decay_up": TensorDecl((heads * dk, spec.decay_rank)),
-            "gate_down": TensorDecl((spec.gate_rank, spec.model_dim)),
-            "gate_up": TensorDecl((heads * dv, spec.gate_rank)),
+            "dt_bias": TensorDecl((decay_columns,), role="vector"),
+            **logits,
             "out_norm": TensorDecl((dv,), role="vector", init="ones"),
             "out_proj": TensorDecl((spec.model_dim, heads * dv)),
         }
@@ -103,8 +129,11 @@ class GatedDelta(Mixer):
         lists, host_lists = step.plan_of(self)
         chunk_plan = dict(lists, num_chunks=host_lists["chunk_start"].size, num_long=host_lists["long_table"].size // 3, num_direct=host_lists["direct"].size)
         proj = ops.linear(x, self.in_proj, status=status)
-        low = ops.linear(x, self.low_rank_down, status=status)
-        logits = ops.linear(low, self.low_rank_up, status=status)
+        if self.direct:
+            logits = proj[:, self.decay_offset :]
+        else:
+            low = ops.linear(x, self.low_rank_down, status=status)
+            logits = ops.linear(low, self.low_rank_up, status=status)
         read_out = ops.gated_delta_rule(
             proj,
             logits,
@@ -127,5 +156,8 @@ class GatedDelta(Mixer):
             segments=step.segments,
             status=status,
             chunk_plan=chunk_plan,
+            decay_per_head=not spec.decay_per_channel,
+            gate_activation=spec.gate_activation,
+            gate_offset=self.gate_offset,
         )
         return ops.linear(read_out, self.out_proj, status=status)

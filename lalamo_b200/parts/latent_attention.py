@@ -30,11 +30,20 @@ class LatentAttention(Mixer):
             raise ValueError(f"window must be positive, got {spec.window}")
         if not isinstance(spec.latent_norm, RMSNormSpec) or spec.latent_norm.dim != spec.latent_dim:
             raise ValueError("the latent vector's norm must be an RMS norm over latent_dim")
-        if not isinstance(spec.position, RopeSpec) or spec.position.rotary_dim != spec.rope_dim or spec.position.pairing != "half":
-            raise ValueError("latent attention rotates all rope_dim channels of the rotated parts, channel i with i + rope_dim / 2")
+        if not isinstance(spec.position, RopeSpec) or spec.position.rotary_dim != spec.rope_dim or spec.position.pairing not in ("half", "interleaved"):
+            raise ValueError("latent attention rotates all rope_dim channels of the rotated parts, in halves or in pairs of neighbours")
         heads, dim, rope = spec.num_heads, spec.head_dim, spec.rope_dim
+        q_proj, down_proj = tensors["q_proj"], tensors["down_proj"]
+        if spec.position.pairing == "interleaved":
+            # The kernels rotate channel i with i + rope / 2.  A score sums over the rotated channels of the query and of the
+            # shared key part, so taking both in the same other order (even channels first, then the odd ones) changes no
+            # score, and pair (2i, 2i + 1) becomes pair (i, i + rope / 2) with its angle.
+            order = torch.cat([torch.arange(0, rope, 2), torch.arange(1, rope, 2)])
+            per_head = q_proj.reshape(heads, dim + rope, -1)
+            q_proj = torch.cat([per_head[:, :dim], per_head[:, dim:][:, order]], dim=1).reshape(q_proj.shape)
+            down_proj = torch.cat([down_proj[: spec.latent_dim], down_proj[spec.latent_dim :][order]], dim=0)
         # One product for everything that reads the mixer's input: queries, the gate, the latent's down-projection.
-        rows = [tensors["q_proj"]] + ([tensors["gate_proj"]] if spec.gated else []) + [tensors["down_proj"]]
+        rows = [q_proj] + ([tensors["gate_proj"]] if spec.gated else []) + [down_proj]
         self.in_proj = runtime.matrix(torch.cat(rows, dim=0))
         self.q_width = heads * (dim + rope)
         self.gate_width = heads * spec.value_dim if spec.gated else 0
@@ -42,7 +51,10 @@ class LatentAttention(Mixer):
         self.value_up = runtime.matrix(tensors["value_up_proj"].reshape(heads, spec.value_dim, spec.latent_dim))
         self.out_proj = runtime.matrix(tensors["out_proj"])
         self.latent_norm = runtime.vector(tensors["latent_norm"])
+        self.sink = runtime.vector(tensors["sink"]) if spec.sink else None
         self.position = build_part(spec.position, {}, runtime)
+        if self.position.magnitude != 1.0:
+            raise ValueError("latent attention takes no factor on sines and cosines")
         self.scale = spec.scale if spec.scale is not None else (dim + rope) ** -0.5
 
     @classmethod
@@ -58,6 +70,8 @@ class LatentAttention(Mixer):
         }
         if spec.gated:
             decls["gate_proj"] = TensorDecl((heads * spec.value_dim, spec.model_dim))
+        if spec.sink:
+            decls["sink"] = TensorDecl((heads,), role="vector")
         return decls
 
     def cache_need(self) -> CacheNeed | None:
@@ -104,7 +118,7 @@ class LatentAttention(Mixer):
                            write_kv=cache.owns, status=runtime.status)
         summed = runtime.empty(tokens, heads, latent)
         common = dict(positions=step.positions, token_segment=step.token_segment, block_table=cache.block_table, num_heads=heads, latent=latent, rope=rope,
-                      scale=self.scale, window=spec.window, status=runtime.status)
+                      scale=self.scale, window=spec.window, status=runtime.status, sink=self.sink)
         if ops.latent_attention_supported(runtime.dtype, latent, rope, cache.k_pages.shape[1]):
             lists, host_lists = step.plan_of(self)
             num_items = host_lists["items"].size // 2

@@ -30,6 +30,9 @@ def plan_tensor_decls(plan: ModelPlan) -> dict[TensorKey, TensorDecl]:
     for index, layer in enumerate(plan.layers):
         for (role, local), decl in block_tensor_decls(layer).items():
             decls[(("layers", index, role), local)] = decl
+    if plan.stream_mix is not None:
+        for local, decl in part_type(plan.stream_mix).tensor_decls(plan.stream_mix).items():
+            decls[(("stream_mix",), local)] = decl
     for local, decl in part_type(plan.final_norm).tensor_decls(plan.final_norm).items():
         decls[(("final_norm",), local)] = decl
     for local, decl in part_type(plan.head).tensor_decls(plan.head).items():
@@ -55,6 +58,10 @@ class DecoderModel:
                 if len(path) == 3 and path[0] == "layers" and path[1] == index
             }
             self.blocks.append(build_block(layer, block_tensors, runtime))
+        self.stream_mix = None
+        if plan.stream_mix is not None:
+            mix_tensors = {local: tensor for (path, local), tensor in tensors.items() if path == ("stream_mix",)}
+            self.stream_mix = build_part(plan.stream_mix, mix_tensors, runtime)
         final_tensors = {local: tensor for (path, local), tensor in tensors.items() if path == ("final_norm",)}
         self.final_norm: Norm = build_part(plan.final_norm, final_tensors, runtime)  # type: ignore[assignment]
 
@@ -100,6 +107,8 @@ class DecoderModel:
             visit(self.blocks[entry.layer])
         visit(self.final_norm)
         visit(self.head)
+        if self.stream_mix is not None:
+            visit(self.stream_mix)
         return sum(seen.values())
 
     def forward(self, step: StepInputs, caches: list[CacheView | None]) -> torch.Tensor:
@@ -113,9 +122,15 @@ class DecoderModel:
                     pending = None
                 step.carry.clear()   # what a block left for its successor described the stream before this sum
                 self.embedding.add_to(residual, step.token_ids)
+            if entry.mix_embedding:
+                if pending is not None:
+                    ops.residual_add(residual, pending)
+                    pending = None
+                step.carry.clear()   # as above: the stream is another one from here on
+                residual = self.stream_mix.forward(residual, self.embedding, step.token_ids)
             # the norm the next block begins with, for a block that can compute it on its way out
             following = self.plan.schedule[position + 1] if position + 1 < len(self.plan.schedule) else None
-            step.carry["next_norm"] = None if following is None or following.add_embedding else getattr(self.blocks[following.layer], "first_norm", None)
+            step.carry["next_norm"] = None if following is None or following.add_embedding or following.mix_embedding else getattr(self.blocks[following.layer], "first_norm", None)
             pending = self.blocks[entry.layer].forward(residual, pending, step, caches[position])
         if step.wanted == 0:
             return runtime.empty(0, self.plan.vocab_size, dtype=torch.float32)
