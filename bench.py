@@ -308,7 +308,7 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
     layer (of a routed feed-forward the router and the experts a token uses), attention (a multiply-add per query, visible
     key and channel, for scores and for values, under the window if there is one), the delta rule's three passes over a
     head's state per token, and the read-out of the wanted rows."""
-    from lalamo_b200.config import AttentionSpec, GatedDeltaSpec, GatedMLPSpec, LatentAttentionSpec, ParallelMixerSpec, RoutedMLPSpec, ShortConvSpec
+    from lalamo_b200.config import AttentionSpec, DenseMLPSpec, GatedDeltaSpec, GatedMLPSpec, LatentAttentionSpec, ParallelMixerSpec, RoutedMLPSpec, ShortConvSpec
 
     def mixer_flops(spec) -> float:
         if isinstance(spec, ParallelMixerSpec):
@@ -329,6 +329,8 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
         if isinstance(spec, GatedDeltaSpec):
             inner = spec.num_heads * (spec.key_dim + spec.value_dim)
             rows = 2 * spec.num_groups * spec.key_dim + 2 * spec.num_heads * spec.value_dim + spec.num_heads + spec.decay_rank + spec.gate_rank
+            if spec.decay_rank == 0:   # decay and gate logits are rows of the in-projection
+                rows += spec.num_heads * (spec.key_dim if spec.decay_per_channel else 1) + spec.num_heads * spec.value_dim
             per_token = 2.0 * rows * spec.model_dim + 2.0 * inner * max(spec.decay_rank, spec.gate_rank) + 8.0 * spec.num_heads * spec.key_dim * spec.value_dim
             return per_token * tokens
         if isinstance(spec, ShortConvSpec):
@@ -340,6 +342,8 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
             return 0.0
         if isinstance(spec, GatedMLPSpec):
             return 2.0 * 3 * spec.model_dim * spec.hidden_dim * tokens
+        if isinstance(spec, DenseMLPSpec):
+            return 2.0 * 2 * spec.model_dim * spec.hidden_dim * tokens
         if isinstance(spec, RoutedMLPSpec):
             return 2.0 * (3 * spec.top * spec.hidden_dim + spec.num_experts) * spec.model_dim * tokens + ffn_flops(spec.shared)
         raise TypeError(f"no operation count for {type(spec).__name__}")
@@ -348,13 +352,17 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
     for entry in plan.schedule:
         layer = plan.layers[entry.layer]
         total += mixer_flops(layer.mixer) + ffn_flops(layer.ffn)
+        if entry.mix_embedding:
+            total += 2.0 * 2 * plan.model_dim * plan.model_dim * tokens
     return total
 
 
-def run_compare(arguments, peaks: dict, peak_source: str, families: tuple[str, str] = ("vuvulorn", "lfm2")) -> int:
+def run_compare(arguments, peaks: dict, peak_source: str, families: tuple[str, ...] = ("vuvulorn", "lfm2")) -> int:
     """`--config vuvulorn-compare`: the Vuvulorn shapes beside the LFM2 shapes of the same width and depth (random weights):
     a prompt of 2,048 tokens in one step, and decode steps at batch 8 and 64 with 4,096 tokens behind every request.
-    `--config tudulix-compare`: the same for the Tudulix shapes beside the Vuvulorn shapes."""
+    `--config tudulix-compare`: the same for the Tudulix shapes beside the Vuvulorn shapes.
+    `--config vivulorn-compare`: the Vivulorn shapes beside the Tudulix shapes (attention, latent attention, a repeated stretch)
+    and the Vuvulorn shapes (the delta rule, dense feed-forwards)."""
     import torch
 
     from lalamo_b200.config import config_from_dict
@@ -535,8 +543,8 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=500)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--compare-sizes", default="350m,1.2b", help="the sizes --config vuvulorn-compare and tudulix-compare measure")
-    parser.add_argument("--config", default="lfm2-1.2b-decode", choices=["lfm2-1.2b-decode", "lfm2-350m-mixed", "lfm2-700m-long", "vuvulorn-compare", "tudulix-compare"],
+    parser.add_argument("--compare-sizes", default="350m,1.2b", help="the sizes --config vuvulorn-compare, tudulix-compare and vivulorn-compare measure")
+    parser.add_argument("--config", default="lfm2-1.2b-decode", choices=["lfm2-1.2b-decode", "lfm2-350m-mixed", "lfm2-700m-long", "vuvulorn-compare", "tudulix-compare", "vivulorn-compare"],
                         help="lfm2-1.2b-decode (default): the decode step and its points; lfm2-350m-mixed: 64 requests with prompts of 128 to 2,048 "
                              "tokens and 256 new tokens through the scheduler; lfm2-700m-long: 16,384-token prompts at batch 1 and 8, then 512 decode steps")
     parser.add_argument("--batch", type=int, default=8)
@@ -577,6 +585,8 @@ def main() -> int:
         return run_compare(arguments, peaks, peak_source)
     if arguments.config == "tudulix-compare":
         return run_compare(arguments, peaks, peak_source, families=("tudulix", "vuvulorn"))
+    if arguments.config == "vivulorn-compare":
+        return run_compare(arguments, peaks, peak_source, families=("vivulorn", "tudulix", "vuvulorn"))
     if arguments.requests:
         requests, prompt_length, new_tokens = (int(part) for part in arguments.requests.split(","))
         engine, config = build_engine(max_tokens=requests * (prompt_length + new_tokens + 64), max_requests=max(requests, 2), max_batch_tokens=2048)

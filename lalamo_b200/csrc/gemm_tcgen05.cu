@@ -37,7 +37,17 @@ struct TcParams {
     int bulk_store;     // the walking kernel writes its output by bulk tensor stores (rows of the output 16-byte aligned)
     int early_successor;   // the one-tile kernel lets the kernel after it start before it has finished
     int* status;
+    const float* bias;     // kTcStore with store_activation >= 0: one per row of W (may be null), added in 32-bit
+    int store_activation;  // kTcStore: -1 stores the sums; 0 silu, 1 gelu (erf), 2 identity of (sum + bias), rounded once
 };
+
+// What a kTcStore epilogue with an activation stores for a sum: act(sum + bias).
+__device__ __forceinline__ float tc_store_value(float sum, float bias, int activation) {
+    const float v = sum + bias;
+    if (activation == 0) return v / (1.0f + expf(-v));
+    if (activation == 1) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+    return v;
+}
 
 // The two sides of a gated epilogue: hidden = tc_up_side(up) * tc_gate_side(gate).  Activations 0 to 2 are act(gate) * up;
 // activation 3 is min(gate, limit) * sigmoid(1.702 min(gate, limit)) * (clamp(up, -limit, limit) + 1).
@@ -171,6 +181,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (!ok) atomicExch(&failed, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const bool as_bfloat16 = p.epilogue == kTcStore || gated;
+        const bool transformed = p.epilogue == kTcStore && p.store_activation >= 0;
+        const float bias_here = transformed && p.bias != nullptr && row0 + local_row < p.n ? p.bias[row0 + local_row] : 0.0f;
         // Turned tile: [BN tokens][128 rows] of bfloat16 or float32, rows padded against bank conflicts.
         constexpr int kPitchHalf = kTcRows + 8, kPitchFloat = kTcRows + 4;
         if (ok) {
@@ -192,7 +204,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    if (as_bfloat16) reinterpret_cast<__nv_bfloat16*>(tiles)[(column + i) * kPitchHalf + local_row] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                    if (transformed) reinterpret_cast<__nv_bfloat16*>(tiles)[(column + i) * kPitchHalf + local_row] = __float2bfloat16_rn(tc_store_value(__uint_as_float(v[i]), bias_here, p.store_activation));
+                    else if (as_bfloat16) reinterpret_cast<__nv_bfloat16*>(tiles)[(column + i) * kPitchHalf + local_row] = __float2bfloat16_rn(__uint_as_float(v[i]));
                     else reinterpret_cast<float*>(tiles)[(column + i) * kPitchFloat + local_row] = __uint_as_float(v[i]);
                 }
             }
@@ -503,6 +516,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
             // products.  Onto the residual stream the box is added in the memory system.
             const bool wide = p.epilogue == kTcStoreFloat || p.epilogue == kTcResidualAdd || p.epilogue == kTcPartial;
             const int step = wide ? 16 : 32;
+            // A thread's row of W is the same for all the item's tokens: its bias is read once.
+            const bool transformed = p.epilogue == kTcStore && p.store_activation >= 0;
+            const float bias_here = transformed && p.bias != nullptr && row0 + quarter * 32 + lane < p.n ? p.bias[row0 + quarter * 32 + lane] : 0.0f;
 #pragma unroll 1
             for (int column = 0; p.bulk_store && column < BN / 2; column += step, ++groups) {
                 if (token0 + column >= p.tokens) break;   // the same for the whole half
@@ -522,7 +538,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                     tmem_load_32(tmem_d + static_cast<uint32_t>(column), v);
                     __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(out_buffer) + quarter * 32 + lane;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) stage[i * kTcRows] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                    for (int i = 0; i < 32; ++i)
+                        stage[i * kTcRows] = __float2bfloat16_rn(transformed ? tc_store_value(__uint_as_float(v[i]), bias_here, p.store_activation) : __uint_as_float(v[i]));
                 } else {
                     // Lanes 0-63 of the accumulator are rows of `up`, lanes 64-127 the same rows of `gate`:
                     // the warp with the gates activates them and hands them over (two buffers, a barrier
@@ -641,7 +658,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                             __nv_bfloat16* destination = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(token0 + column) * p.n + row;
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
-                                if (whole || i < tokens_here) destination[static_cast<size_t>(i) * p.n] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                                if (whole || i < tokens_here)
+                                    destination[static_cast<size_t>(i) * p.n] =
+                                        __float2bfloat16_rn(transformed ? tc_store_value(__uint_as_float(v[i]), bias_here, p.store_activation) : __uint_as_float(v[i]));
                         } else if (p.epilogue == kTcStoreFloat || p.epilogue == kTcPartial) {
                             float* destination = static_cast<float*>(p.out) + (static_cast<size_t>(slice) * p.tokens + token0 + column) * p.n + row;
 #pragma unroll
@@ -874,9 +893,13 @@ long long lb_gemm_tcgen05_scratch_floats(int tokens, int n, int slices) {
 // aligned; tokens < 1), -3 if the scratch is too small, -5 if no tensor map could be made.
 // defer_sum: with more than one slice, leave the partial sums in `scratch` ([slices][tokens][n]) for the
 // caller (lb_sum_slices, or a consumer that adds them itself); `out` is not touched then.
-int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, long long scratch_floats, int tokens, int k, int n, int epilogue,
-                    int activation, int slices, int defer_sum, int* status, cudaStream_t stream, float limit) {
+static int gemm_tcgen05_launch(const void* x, const void* w, void* out, float* scratch, long long scratch_floats, int tokens, int k, int n, int epilogue,
+                               int activation, int slices, int defer_sum, int* status, cudaStream_t stream, float limit, const float* bias, int store_activation) {
     if (tokens < 1 || n < 1 || k < 8 || k % 8 != 0 || epilogue < 0 || epilogue == 3 || epilogue > 4) return -2;
+    if (store_activation >= 0) {
+        if (epilogue != lb::kTcStore || store_activation > 2) return -2;
+        slices = 1;   // the bias and the activation belong to the whole sum
+    }
     if (epilogue == lb::kTcGated) {
         if (n % 2 != 0) return -2;
         slices = 1;
@@ -896,6 +919,8 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     p.limit = limit;
     p.bulk_store = 0;
     p.early_successor = tokens > 16 ? 1 : 0;
+    p.bias = bias;
+    p.store_activation = store_activation;
     if (slices > 1) {
         if (scratch == nullptr || lb_gemm_tcgen05_scratch_floats(tokens, n, slices) > scratch_floats) return -3;
         p.out = scratch;
@@ -953,6 +978,19 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     else code = lb::launch_tcgen05<128>(map_w, x, p, slices, stream);
     if (code != 0 || slices == 1 || defer_sum) return code;
     return lb_sum_slices(scratch, out, tokens, n, slices, epilogue, stream);
+}
+
+int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, long long scratch_floats, int tokens, int k, int n, int epilogue,
+                    int activation, int slices, int defer_sum, int* status, cudaStream_t stream, float limit) {
+    return gemm_tcgen05_launch(x, w, out, scratch, scratch_floats, tokens, k, n, epilogue, activation, slices, defer_sum, status, stream, limit, nullptr, -1);
+}
+
+// out[t, r] = bfloat16(act(sum_k x[t, k] w[r, k] + bias[r])): the sum, the bias (32-bit, may be null) and the activation
+// (0 silu, 1 exact gelu, 2 identity) in 32-bit, rounded once, in the product's epilogue.  One K slice.  Return codes as above.
+int lb_gemm_tcgen05_bias_activation(const void* x, const void* w, const float* bias, void* out, int tokens, int k, int n, int activation, int* status,
+                                    cudaStream_t stream) {
+    if (activation < 0 || activation > 2) return -2;
+    return gemm_tcgen05_launch(x, w, out, nullptr, 0, tokens, k, n, lb::kTcStore, 2, 1, 0, status, stream, 0.0f, bias, activation);
 }
 
 // out = epilogue(partials[0] + partials[1] + ...), the slices added in order; partials is [slices][tokens][n].

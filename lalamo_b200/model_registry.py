@@ -146,6 +146,29 @@ def _tudulix_shape(width: int, layers: int, heads: int, kv_heads: int, ff: int, 
     }
 
 
+def _vivulorn_shape(width: int, layers: int, heads: int, kv_heads: int, delta_heads: int, delta_dim: int, delta_vdim: int, ff: int, rank: int) -> dict[str, Any]:
+    """A Vivulorn shape for the random-weights mode: layers in the order attention, delta rule, latent attention, delta rule;
+    attention with heads of 64 and stretched rotation, latent attention with heads of 64 + 32 rotated channels over a latent of
+    ``rank``, the delta rule with ``delta_heads`` heads over half as many key heads behind convolutions of four taps; every layer
+    but each second delta layer with a dense feed-forward of ``ff`` columns; the third and fourth layer run twice."""
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125,
+                 "rot": {"dims": 64, "base": 1000000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    latent = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": rank, "scale": 96 ** -0.5, "rot": {"dims": 32, "base": 10000.0}}
+    delta = {"heads": delta_heads, "kv_heads": delta_heads // 2, "dim": delta_dim, "vdim": delta_vdim, "conv": 4}
+    kinds = [("attention", attention), ("delta", delta), ("latent_attention", latent), ("delta", delta)]
+    dense = {"kind": "dense", "ff": ff}
+    return {
+        "architecture": "Vivulorn",
+        "vocab": 65536,
+        "width": width,
+        "norm": {"eps": 1e-5},
+        "embedding": {"scale": float(width) ** 0.5},
+        "logit_softcap": 30.0,
+        "loop": {"start": 2, "stop": 4, "times": 2},
+        "layers": [{"type": kinds[index % 4][0], "mixer": kinds[index % 4][1], "mlp": None if index % 8 == 7 else dense} for index in range(layers)],
+    }
+
+
 # Shapes of the published checkpoints, and Vuvulorn shapes of the same widths and depths, for the random-weights mode
 # (no weights are downloaded).
 PRESETS: dict[str, dict[str, Any]] = {
@@ -157,4 +180,7 @@ PRESETS: dict[str, dict[str, Any]] = {
     # 14 layers of which two run twice: 16 layer runs, and per token as many feed-forward columns (3 routed experts + the shared one) as the shapes above
     "tudulix-350m": _tudulix_shape(1024, 14, 16, 4, 1152, 16, 3, 256),
     "tudulix-1.2b": _tudulix_shape(2048, 14, 16, 4, 2048, 16, 3, 256),
+    # 14 layers of which two run twice (16 layer runs); the two projections of the plain feed-forward hold what the three of a gated one of 4,608 (8,192) columns hold
+    "vivulorn-350m": _vivulorn_shape(1024, 14, 16, 4, 8, 64, 128, 6912, 256),
+    "vivulorn-1.2b": _vivulorn_shape(2048, 14, 16, 4, 8, 128, 128, 12288, 256),
 }

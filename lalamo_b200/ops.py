@@ -1503,7 +1503,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
 def linear_bias_activation(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, activation: str,
                            status: torch.Tensor | None = None) -> torch.Tensor:
     """``act(x @ weight.T + bias)`` in ``x``'s type (the sum and the activation in 32-bit, rounded once).  Steps of up to 16
-    tokens compute it in the weight-streaming product's epilogue; other steps run the product, then one elementwise kernel."""
+    tokens compute it in the weight-streaming product's epilogue, other bfloat16 steps in the tcgen05 product's; what neither takes
+    (32-bit, widths that are no multiples of 8) runs the product, then one elementwise kernel."""
     _check(x, "x")
     _check(weight, "weight", x.dtype)
     if activation not in ("silu", "gelu", "identity"):
@@ -1517,6 +1518,14 @@ def linear_bias_activation(x: torch.Tensor, weight: torch.Tensor, bias: torch.Te
     if skinny_supported(x, weight.shape[0]):
         out = torch.empty(x.shape[0], weight.shape[0], dtype=x.dtype, device=x.device)
         _skinny(x, weight, out, weight.shape[0], "store", activation, bias=bias)
+        return out
+    if USE_TCGEN05 and tcgen05_supported(x, weight.shape[0]):
+        out = torch.empty(x.shape[0], weight.shape[0], dtype=x.dtype, device=x.device)
+        code = _lib().lb_gemm_tcgen05_bias_activation(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), c_int(x.shape[0]), c_int(x.shape[1]), c_int(weight.shape[0]),
+                                                      c_int(_ACTIVATIONS[activation]), _ptr(status), _stream())
+        if code == -5:
+            raise KernelError("linear_bias_activation: the driver gave no tensor map (cuTensorMapEncodeTiled)")
+        _done(code, "gemm_tcgen05_bias_activation")
         return out
     product = linear(x, weight, status=status)
     if isinstance(product, SlicedSum):

@@ -738,6 +738,33 @@ def test_tcgen05_gated(ops, tokens, width, hidden, activation):
     close(got, up * rnd(act, torch.bfloat16), torch.bfloat16, scale=2)
 
 
+@pytest.mark.parametrize("tile", [None, "64", "128", "256", "512"])
+@pytest.mark.parametrize("tokens,width,rows,activation,with_bias", [
+    (3, 64, 200, "gelu", True), (17, 64, 128, "gelu", True), (40, 328, 1000, "silu", True), (100, 512, 6144, "gelu", False), (129, 72, 120, "gelu", True),
+    (300, 96, 134, "identity", True), (700, 1024, 2600, "gelu", True), (2100, 328, 2600, "silu", False), (260, 100, 96, "gelu", True),
+])
+def test_linear_with_bias_and_activation(ops, monkeypatch, tile, tokens, width, rows, activation, with_bias):
+    """``act(x W^T + b)`` rounded once: the weight-streaming product's epilogue for few tokens, the tcgen05 products' (the
+    one-tile kernel, every tile of the walking kernel, outputs that leave by bulk stores and outputs that cannot), and, where
+    the width is no multiple of 8, a library product followed by the elementwise kernel; in both types."""
+    if tile is not None:
+        if tokens <= 128:
+            pytest.skip("the walking kernel's tiles are for more than 128 tokens")
+        monkeypatch.setenv("LALAMO_B200_TCGEN05_TILE", tile)
+    generator = torch.Generator().manual_seed(tokens + rows)
+    x = torch.randn(tokens, width, generator=generator).to(torch.bfloat16)
+    w = (2.0 * torch.randn(rows, width, generator=generator) / math.sqrt(width)).to(torch.bfloat16)
+    bias = torch.randn(rows, generator=generator) if with_bias else None
+    summed = x.double() @ w.double().T + (bias.double() if with_bias else 0.0)
+    want = {"gelu": 0.5 * summed * (1 + torch.erf(summed / math.sqrt(2))), "silu": summed * torch.sigmoid(summed), "identity": summed}[activation]
+    got = ops.linear_bias_activation(dev(x), dev(w), dev(bias) if with_bias else None, activation)
+    assert got.shape == (tokens, rows) and got.dtype == torch.bfloat16
+    close(got, want, torch.bfloat16, scale=2)
+    if tile is None:
+        got = ops.linear_bias_activation(dev(x.float()), dev(w.float()), dev(bias) if with_bias else None, activation)
+        torch.testing.assert_close(got.cpu().double(), want, rtol=1e-4, atol=1e-4)
+
+
 @pytest.mark.parametrize("tile", ["64", "128", "256", "512"])
 @pytest.mark.parametrize("tokens,width,rows", [(300, 200, 384), (1000, 2048, 640), (2100, 328, 2600), (513, 72, 130)])
 def test_tcgen05_walking_tiles(ops, monkeypatch, tile, tokens, width, rows):
