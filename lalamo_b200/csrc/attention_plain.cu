@@ -54,6 +54,7 @@ struct RewriteExtras {
     const float* row_inv;
     float turn_scale;   // sines and cosines are multiplied by this
     int row_stride;     // elements between the rows of qkv (>= the q, k and v columns; what follows them is not read)
+    int inline_whole;   // the warp-per-head kernel computes the projection-wide statistic itself (row_inv is then only a flag)
 };
 
 // grid (tokens, num_heads + num_groups), one warp per head vector.
@@ -106,7 +107,19 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
     }
 
     float inv = 1.0f;
-    if (whole) {
+    if (whole && extra.inline_whole) {
+        // For few tokens every warp sums its token's whole projection itself, in the order projection_inv_rms_kernel
+        // uses (the same bits): a few KB from L2 per warp instead of a launch.
+        const int columns = (is_query ? num_heads : layout.num_groups) * hd;
+        const T* all = qkv + static_cast<size_t>(token) * width + (is_query ? 0 : static_cast<size_t>(num_heads) * hd);
+        float sum = 0.0f;
+        for (int d = lane; d < columns; d += 32) {
+            const float v = to_float(all[d]);
+            sum += v * v;
+        }
+        sum = warp_sum(sum);
+        inv = rsqrtf(sum / static_cast<float>(columns) + eps);
+    } else if (whole) {
         inv = extra.row_inv[2 * static_cast<size_t>(token) + (is_query ? 0 : 1)];
     } else if (weight != nullptr) {
         float sum = 0.0f;
@@ -624,8 +637,9 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
     const int columns = (num_heads + num_groups) * head_dim + num_groups * value_dim;
     if (row_stride <= 0) row_stride = columns;
     if (row_stride < columns || (row_inv != nullptr && (q_weight == nullptr || bias != nullptr))) return -2;
-    const lb::RewriteExtras extra{row_inv, turn_scale, row_stride};
-    if (row_inv != nullptr) {
+    const int inline_whole = row_inv != nullptr && tokens <= 64 ? 1 : 0;   // the warp-per-head kernel below
+    const lb::RewriteExtras extra{row_inv, turn_scale, row_stride, inline_whole};
+    if (row_inv != nullptr && !inline_whole) {
         LB_DISPATCH_DTYPE(dtype, {
             lb::projection_inv_rms_kernel<T><<<dim3(tokens, 2), 32, 0, stream>>>(static_cast<const T*>(qkv), row_stride, num_heads * head_dim,
                                                                                  num_groups * head_dim, eps, row_inv);

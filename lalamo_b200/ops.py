@@ -544,7 +544,7 @@ def qk_norm_rope_write(
         _ptr(inv_freq), c_int(rotary_dim), _ptr(positions), _ptr(token_segment), _ptr(block_table), c_int(tokens), c_int(num_heads),
         c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks), c_int(1 if write_kv else 0),
         c_int(dtype_code(qkv.dtype)), _ptr(status), _stream(), c_int(value_dim), _ptr(bias), _ptr(row_inv), c_float(turn_scale), c_int(qkv.stride(0)))
-    _done(code, "qk_norm_rope_write", 2 if whole_norm else 1)
+    _done(code, "qk_norm_rope_write", 2 if whole_norm and tokens > 64 else 1)   # few tokens: the statistic is computed in the rewrite itself
 
 
 def paged_attention_plain(

@@ -257,6 +257,56 @@ def check_qk_norm_rope_write(ops, dtype, segments, heads, groups, head_dim, rota
     assert (k_host[~written] == 99.0).all() and (v_host.permute(0, 3, 1, 2)[~written] == 99.0).all()  # nothing else was touched
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("tokens_kind", ["few", "many", "runs"])  # a warp per head that sums the projection itself / a block per token / four tokens a block
+@pytest.mark.parametrize("heads,groups,head_dim,value_dim,rotary,extra_columns", [
+    (6, 3, 64, 64, 64, 384), (4, 2, 16, 32, 8, 128), (3, 3, 24, 8, 0, 0), (5, 1, 32, 16, 20, 80), (16, 4, 64, 64, 64, 1024), (2, 1, 12, 20, 12, 40),
+])
+def test_qk_rewrite_with_a_norm_over_the_whole_projection(ops, dtype, tokens_kind, heads, groups, head_dim, value_dim, rotary, extra_columns):
+    """One RMS statistic over all of a token's query columns and one over all of its key columns, weights of one element per
+    column, 32-bit until the one rounding after the rotation; sines and cosines scaled; values of their own size; q, k and v
+    as the first columns of a wider product."""
+    page_size, eps, turn_scale = 16, 1e-5, 1.0693
+    segments = {"few": [(0, 21), (37, 1), (15, 3), (5000, 2)], "many": [(0, 21), (37, 1), (15, 3), (200, 90)], "runs": [(0, 300), (37, 1), (15, 3), (8, 120), (203, 250)]}[tokens_kind]
+    generator = torch.Generator().manual_seed(heads * 100 + head_dim)
+    table, positions, token_segment, num_pages = paged_setup(segments, page_size, generator)
+    tokens = positions.numel()
+    q_columns, k_columns, v_columns = heads * head_dim, groups * head_dim, groups * value_dim
+    product = (torch.randn(tokens, q_columns + k_columns + v_columns + extra_columns, generator=generator) * (1 + torch.arange(tokens)[:, None] % 5)).to(dtype)
+    q_weight, k_weight = 1 + 0.3 * torch.randn(q_columns, generator=generator), 1 + 0.3 * torch.randn(k_columns, generator=generator)
+    inv_freq = (1.0 / (torch.tensor(300.0) ** (torch.arange(0, rotary, 2).float() / rotary))) if rotary else None
+    k_pages = torch.full((num_pages, page_size, groups, head_dim), 99.0, dtype=dtype, device="cuda")
+    v_pages = torch.full((num_pages, groups, value_dim, page_size), 99.0, dtype=dtype, device="cuda")
+    q_out = torch.empty(tokens, q_columns, dtype=dtype, device="cuda")
+    flag = status()
+    on_device = dev(product)
+    ops.qk_norm_rope_write(
+        on_device[:, : q_columns + k_columns + v_columns], q_out, k_pages, v_pages, q_weight=dev(q_weight), k_weight=dev(k_weight), eps=eps, scale_offset=0.0,
+        inv_freq=None if inv_freq is None else dev(inv_freq), rotary_dim=rotary, positions=dev(positions), token_segment=dev(token_segment), block_table=dev(table),
+        num_heads=heads, num_groups=groups, head_dim=head_dim, write_kv=True, status=flag, value_dim=value_dim, whole_norm=True, turn_scale=turn_scale)
+    assert flag.item() == 0
+
+    def transform(x: torch.Tensor, weight: torch.Tensor, count: int) -> torch.Tensor:
+        x = x.double()
+        x = (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.double()).reshape(tokens, count, head_dim)
+        if not rotary:
+            return x
+        angles = (positions.float()[:, None] * inv_freq[None, :]).double()
+        cos, sin = turn_scale * torch.cos(angles)[:, None, :], turn_scale * torch.sin(angles)[:, None, :]
+        first, second, tail = x[..., : rotary // 2], x[..., rotary // 2 : rotary], x[..., rotary:]
+        return torch.cat([first * cos - second * sin, second * cos + first * sin, tail], dim=-1)
+
+    close(q_out.reshape(tokens, heads, head_dim), transform(product[:, :q_columns], q_weight, heads), dtype, scale=6)
+    k_expected = transform(product[:, q_columns : q_columns + k_columns], k_weight, groups)
+    v = product[:, q_columns + k_columns : q_columns + k_columns + v_columns].reshape(tokens, groups, value_dim)
+    k_host, v_host = k_pages.cpu(), v_pages.cpu()
+    for t in range(tokens):
+        position, segment = int(positions[t]), int(token_segment[t])
+        page, row = int(table[segment, position // page_size]), position % page_size
+        close(k_host[page, row], k_expected[t], dtype, scale=6)
+        assert torch.equal(v_host[page, :, :, row], v[t])
+
+
 def reference_attention(q, keys, values, position, scale, window):
     """One query [heads, hd] at `position` against keys/values [len, groups, hd] of its request."""
     heads, groups = q.shape[0], keys.shape[1]
