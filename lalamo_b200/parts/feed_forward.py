@@ -42,8 +42,9 @@ class GatedMLP(FeedForward):
 @register_part(DenseMLPSpec)
 class DenseMLP(FeedForward):
     """``down(act(up(x) + b_up)) + b_down``: two projections around an activation, no gate.  The up-projection's bias and the
-    activation are the product's epilogue for steps of few tokens (one elementwise kernel after the product otherwise); the
-    down-projection's bias is added with the product, onto the 32-bit stream, by whoever adds it."""
+    activation are the product's epilogue (the weight-streaming product's for steps of few tokens, the tcgen05 product's
+    otherwise; one elementwise kernel after a library product in 32-bit); the down-projection's bias is added with the
+    product, onto the 32-bit stream, by whoever adds it."""
 
     def __init__(self, spec: DenseMLPSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         super().__init__(spec, tensors, runtime)
