@@ -166,10 +166,14 @@ class CacheManager:
                 for entry in group.entries:
                     need = needs[entry]
                     assert isinstance(need, PagedKVNeed)
-                    # keys [page][row][group][channel]; values transposed, [page][group][channel][row]
-                    self.k_pages[entry] = torch.zeros((num_pages, page_size, need.num_groups, need.head_dim), dtype=runtime.dtype, device=runtime.device)
+                    # keys [page][row][group][channel]; values transposed, [page][group][channel][row]; a need of one row for
+                    # every `tokens_per_row` positions gets pages of as many rows as a page's positions can fill
+                    if need.tokens_per_row < 1 or (need.tokens_per_row > 1 and need.window is not None):
+                        raise ValueError("tokens_per_row must be positive, and rows that stand for several positions are kept for good (no window)")
+                    rows = -(-page_size // need.tokens_per_row)
+                    self.k_pages[entry] = torch.zeros((num_pages, rows, need.num_groups, need.head_dim), dtype=runtime.dtype, device=runtime.device)
                     if not need.values_in_keys:
-                        self.v_pages[entry] = torch.zeros((num_pages, need.num_groups, need.value_dim or need.head_dim, page_size), dtype=runtime.dtype, device=runtime.device)
+                        self.v_pages[entry] = torch.zeros((num_pages, need.num_groups, need.value_dim or need.head_dim, rows), dtype=runtime.dtype, device=runtime.device)
             for entry in self.layout.slot_entries:
                 need = needs[entry]
                 assert isinstance(need, SlotStateNeed)
@@ -345,7 +349,8 @@ class CacheManager:
             live = record.length if group.window is None else min(record.length, group.window + group.keep_first)
             for entry in group.entries:
                 pages, values = self.k_pages[entry], self.v_pages.get(entry)
-                total += live * pages.shape[2] * (pages.shape[3] + (values.shape[2] if values is not None else 0)) * pages.element_size()
+                rows = live // self.needs[entry].tokens_per_row
+                total += rows * pages.shape[2] * (pages.shape[3] + (values.shape[2] if values is not None else 0)) * pages.element_size()
         for state in self.states.values():
             total += state[0].numel() * state.element_size()
         return total

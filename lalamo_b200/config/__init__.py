@@ -11,11 +11,13 @@ from .plan import (
     GatedMLPSpec,
     LatentAttentionSpec,
     LayerNormSpec,
+    LinearAttentionSpec,
     MixerSpec,
     ModelPlan,
     NormSpec,
     OutputNormBlockSpec,
     ParallelMixerSpec,
+    PooledWindowAttentionSpec,
     PositionSpec,
     RMSNormSpec,
     RopeSpec,
@@ -29,12 +31,14 @@ from .plan import (
 from .tudulix import TudulixConfig
 from .vivulorn import VivulornConfig
 from .vuvulorn import VuvulornConfig
+from .zozenex import ZozenexConfig
 from .registry import architectures, config_from_dict, load_config, register_architecture
 
 register_architecture("Lfm2ForCausalLM", Lfm2Config)
 register_architecture("Vuvulorn", VuvulornConfig)
 register_architecture("Tudulix", TudulixConfig)
 register_architecture("Vivulorn", VivulornConfig)
+register_architecture("Zozenex", ZozenexConfig)
 
 __all__ = [
     "AttentionSpec",
@@ -47,11 +51,13 @@ __all__ = [
     "LatentAttentionSpec",
     "LayerNormSpec",
     "Lfm2Config",
+    "LinearAttentionSpec",
     "MixerSpec",
     "ModelPlan",
     "NormSpec",
     "OutputNormBlockSpec",
     "ParallelMixerSpec",
+    "PooledWindowAttentionSpec",
     "PositionSpec",
     "RMSNormSpec",
     "RopeSpec",
@@ -65,6 +71,7 @@ __all__ = [
     "VivulornConfig",
     "VuvulornConfig",
     "YarnScaling",
+    "ZozenexConfig",
     "architectures",
     "config_from_dict",
     "load_config",

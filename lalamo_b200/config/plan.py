@@ -27,11 +27,13 @@ __all__ = [
     "GatedMLPSpec",
     "LatentAttentionSpec",
     "LayerNormSpec",
+    "LinearAttentionSpec",
     "MixerSpec",
     "ModelPlan",
     "NormSpec",
     "OutputNormBlockSpec",
     "ParallelMixerSpec",
+    "PooledWindowAttentionSpec",
     "PositionSpec",
     "RMSNormSpec",
     "RopeSpec",
@@ -195,12 +197,67 @@ class GatedDeltaSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class LinearAttentionSpec(MixerSpec):
+    """Linear attention with a decaying matrix state per head and neither softmax nor denominator:
+    ``S_t = diag(a_t) S_(t-1) + k_t v_t^T; o_t = S_t^T q_t`` with q, k of ``key_dim`` and v of ``value_dim`` channels per head,
+    plain projections of the mixer's input; one of q and k (``scaled``: ``"query"`` or ``"key"``) is multiplied by
+    ``key_dim ** -0.5``.  The decay is fixed, one number per head (``decay="fixed"``, ``decay_values``), or made from the
+    token, one number per head and key channel (``decay="channel"``): ``a = sigmoid(z) ** (1 / tau)`` with
+    ``z = W_a2 (W_a1 h) + b`` through a bottleneck of ``decay_rank``.  Each head's read-out is divided by its root mean
+    square (``norm_eps``; times a weight of ``value_dim`` elements shared by the heads if ``norm_weight``), the heads are
+    multiplied by ``silu(W_g h)`` (or ``sigmoid``, ``gate_activation``) and projected out.  State, decays and their logarithms,
+    the recurrence's inputs and the read-out norm are 32-bit."""
+
+    kind: ClassVar[str] = "linear_attention"
+    model_dim: int = 0
+    num_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    decay: str = "fixed"
+    decay_values: tuple[float, ...] = ()
+    decay_rank: int = 0
+    tau: float = 1.0
+    scaled: str = "key"
+    norm_weight: bool = False
+    norm_eps: float = 1e-5
+    gate_activation: str = "silu"
+
+
+@dataclass(frozen=True)
+class PooledWindowAttentionSpec(MixerSpec):
+    """Grouped attention whose weights are sigmoids, not a softmax, under a sliding window with pooled blocks behind it.
+    Position ``i`` sees the positions ``j`` with ``0 <= i - j < window`` and one mean key and mean value for every block of
+    ``pool`` consecutive positions that lies wholly before the window (block ``b`` covers ``b pool .. b pool + pool - 1`` and
+    is seen if ``b pool + pool - 1 <= i - window``; means of the keys and values as the cache holds them; ``pool=0``: no
+    blocks).  A visible key weighs ``sigmoid(c tanh(q . k scale / c) + bias_h)`` (``softcap`` c, 0: none; ``head_bias``: a
+    learned number per head); the weights are not normalised.  ``position`` rotates q and k; ``rotate_values``: a value is
+    turned by its position over all of its channels (pair ``m`` by ``j theta ** (-2m / value_dim)``, the pairing of
+    ``position``) before it is cached, and a head's sum is turned back by the query's position."""
+
+    kind: ClassVar[str] = "pooled_window_attention"
+    model_dim: int = 0
+    num_heads: int = 0
+    num_groups: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    position: PositionSpec | None = None
+    rotate_values: bool = False
+    window: int = 1
+    pool: int = 0
+    scale: float | None = None  # None -> head_dim ** -0.5
+    softcap: float = 0.0
+    head_bias: bool = False
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec(MixerSpec):
     """Several mixers side by side on the same input; the result is ``sum_i scale_i * branch_i(x)``.
-    ``branches``: ``(name, specification, scale)``; the name prefixes the branch's tensors."""
+    ``branches``: ``(name, specification, scale)``; the name prefixes the branch's tensors.  With ``branch_norm`` every
+    branch's output passes a norm of that specification (a weight of its own per branch, ``<name>.out_norm``) before the sum."""
 
     kind: ClassVar[str] = "parallel"
     branches: tuple[tuple[str, MixerSpec, float], ...] = ()
+    branch_norm: NormSpec | None = None
 
 
 @dataclass(frozen=True)
@@ -252,7 +309,9 @@ class RoutedMLPSpec(FeedForwardSpec):
     ``router_bias``: a bias on the router's logits.  ``score="logits"`` ranks experts by the logits themselves;
     ``chosen_softmax``: the weights are the softmax over the chosen scores only.  ``limit``: of the experts'
     ``"sigmoid_limit"`` activation (see :class:`GatedMLPSpec`).  ``shared``: a dense feed-forward that every token
-    runs besides, added to the experts' weighted sum."""
+    runs besides, added to the experts' weighted sum (``shared_gate``: times ``sigmoid(w_sg . h)``, one number per token).
+    ``gated=False``: the experts are ``down(act(up(x)))`` without a gate.  ``choice_bias``: a learned number per expert added to
+    the scores where experts (and groups) are ranked, not where they weigh.  ``weight_scale`` multiplies the weights."""
 
     kind: ClassVar[str] = "routed_mlp"
     model_dim: int = 0
@@ -267,7 +326,11 @@ class RoutedMLPSpec(FeedForwardSpec):
     router_bias: bool = False
     chosen_softmax: bool = False
     limit: float = 0.0
-    shared: GatedMLPSpec | None = None
+    shared: FeedForwardSpec | None = None
+    gated: bool = True
+    choice_bias: bool = False
+    weight_scale: float = 1.0
+    shared_gate: bool = False
 
 
 @dataclass(frozen=True)
@@ -311,12 +374,13 @@ class BlockSpec:
 @dataclass(frozen=True)
 class EmbeddingSpec:
     """Token embedding: a row of the table per token id, times ``scale``, into the residual stream
-    (``lalamo/modules/embedding.py``)."""
+    (``lalamo/modules/embedding.py``); optionally plus a learned vector per position."""
 
     kind: ClassVar[str] = "token_embedding"
     vocab_size: int = 0
     model_dim: int = 0
     scale: float = 1.0
+    learned_positions: int = 0  # > 0: a table of this many learned position vectors; row ``p`` is added (unscaled) to the token at position ``p``
 
 
 @dataclass(frozen=True)

@@ -425,6 +425,32 @@ __global__ void stream_concat_kernel(const float* __restrict__ stream, const T* 
     }
 }
 
+// residual[r, :] += scale_a * rms_norm(a[r, :]) * weight_a + scale_b * rms_norm(b[r, :]) * weight_b on the 32-bit residual
+// stream, everything in 32-bit (b may be null): the outputs of mixers that run side by side, each normed over the
+// model's width under a weight of its own, then summed.  One block per row.
+template <typename T>
+__global__ void branch_norms_accumulate_kernel(float* __restrict__ residual, const T* __restrict__ a, const float* __restrict__ weight_a, float scale_a,
+                                               const T* __restrict__ b, const float* __restrict__ weight_b, float scale_b, int dim, float eps) {
+    __shared__ float scratch[33];
+    const size_t row = static_cast<size_t>(blockIdx.x) * dim;
+    float sum_a = 0.0f, sum_b = 0.0f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        const float va = to_float(a[row + d]);
+        sum_a += va * va;
+        if (b != nullptr) {
+            const float vb = to_float(b[row + d]);
+            sum_b += vb * vb;
+        }
+    }
+    const float inv_a = rsqrtf(block_sum(sum_a, scratch) / static_cast<float>(dim) + eps);
+    const float inv_b = b != nullptr ? rsqrtf(block_sum(sum_b, scratch) / static_cast<float>(dim) + eps) : 0.0f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float sum = scale_a * (to_float(a[row + d]) * inv_a * weight_a[d]);
+        if (b != nullptr) sum += scale_b * (to_float(b[row + d]) * inv_b * weight_b[d]);
+        residual[row + d] += sum;
+    }
+}
+
 }  // namespace lb
 
 extern "C" {
@@ -566,6 +592,18 @@ int lb_norm_accumulate(float* residual, const void* a, const float* bias_a, floa
         kernel<<<rows, threads, shared, stream>>>(residual, static_cast<const T*>(a), bias_a, scale_a, static_cast<const T*>(b), bias_b, scale_b, weight,
                                                   static_cast<T*>(rounded), dim, eps, scale_offset, next_weight, next_eps, next_offset, pair_out, pair_weight, pair_expert, top,
                                                   experts);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+// b and weight_b may be null (one branch).
+int lb_branch_norms_accumulate(float* residual, const void* a, const float* weight_a, float scale_a, const void* b, const float* weight_b, float scale_b,
+                               int rows, int dim, float eps, int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (b != nullptr && weight_b == nullptr) return -2;
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::branch_norms_accumulate_kernel<T><<<rows, 256, 0, stream>>>(residual, static_cast<const T*>(a), weight_a, scale_a, static_cast<const T*>(b), weight_b,
+                                                                         scale_b, dim, eps);
     })
     return LB_LAUNCH_RESULT();
 }

@@ -177,7 +177,9 @@ __device__ __forceinline__ void scan_copy_16(float* shared_destination, const fl
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(destination), "l"(global_source) : "memory");
 }
 
-template <int DKP, int SPLIT>
+// DELTA false: the plain linear recurrence S <- diag(g_t) S + k_t v_t^T, o_t = S^T q_t (no correction by what the state
+// already holds under k_t, no beta): the same state layout, stages and read-out with a shorter chain per token.
+template <int DKP, int SPLIT, bool DELTA>
 __global__ void __launch_bounds__((kScanCols / kScanThreadCols) * SPLIT)
 gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ g, const float* __restrict__ v,
                 const float* __restrict__ beta, float* __restrict__ state, float* __restrict__ out, const int* __restrict__ segment_start,
@@ -245,7 +247,8 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
             const int tt = index / columns, c = index - tt * columns;
             scan_copy_4(v_of(stage) + tt * kScanCols + c, v + (static_cast<size_t>(start + t0 + tt) * heads + head) * v_columns + col0 + c);
         }
-        for (int tt = tid; tt < n; tt += blockDim.x) scan_copy_4(beta_of(stage) + tt, beta + static_cast<size_t>(start + t0 + tt) * heads + head);
+        if constexpr (DELTA)
+            for (int tt = tid; tt < n; tt += blockDim.x) scan_copy_4(beta_of(stage) + tt, beta + static_cast<size_t>(start + t0 + tt) * heads + head);
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
     fetch(0, 0);
@@ -288,19 +291,21 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
 #pragma unroll
                     for (int c = 0; c < C; ++c) {
                         S[c][i + e] *= decay[e];
-                        dots[c] += S[c][i + e] * key[i + e];
+                        if constexpr (DELTA) dots[c] += S[c][i + e] * key[i + e];
                     }
                 }
             }
+            if constexpr (DELTA) {
 #pragma unroll
-            for (int offset = 1; offset < SPLIT; offset <<= 1) {
+                for (int offset = 1; offset < SPLIT; offset <<= 1) {
 #pragma unroll
-                for (int c = 0; c < C; ++c) dots[c] += __shfl_xor_sync(0xffffffffu, dots[c], offset);
+                    for (int c = 0; c < C; ++c) dots[c] += __shfl_xor_sync(0xffffffffu, dots[c], offset);
+                }
             }
             float u[C], reads[C];
 #pragma unroll
             for (int c = 0; c < C; ++c) {
-                u[c] = beta_s[tt] * (values[c] - dots[c]);
+                u[c] = DELTA ? beta_s[tt] * (values[c] - dots[c]) : values[c];
                 reads[c] = 0.0f;
             }
 #pragma unroll
@@ -491,10 +496,17 @@ template <int DKP, int SPLIT>
 inline void launch_scan(dim3 grid, cudaStream_t stream, const float* q, const float* k, const float* g, const float* v, const float* beta,
                         float* state, float* out, const int* segment_start, const int* segment_length, const int* segment_slot, int heads,
                         int groups, int dk, int dv, int num_slots, int* status, const int* segment_list, int v_columns) {
-    static OncePerDevice once;
-    allow_shared_memory(once, gdr_scan_kernel<DKP, SPLIT>, static_cast<int>(ScanShared<DKP>::kBytes));
-    gdr_scan_kernel<DKP, SPLIT><<<grid, (kScanCols / kScanThreadCols) * SPLIT, ScanShared<DKP>::kBytes, stream>>>(q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot,
-                                                                                      heads, groups, dk, dv, num_slots, status, segment_list, v_columns);
+    if (beta != nullptr) {
+        static OncePerDevice once;
+        allow_shared_memory(once, gdr_scan_kernel<DKP, SPLIT, true>, static_cast<int>(ScanShared<DKP>::kBytes));
+        gdr_scan_kernel<DKP, SPLIT, true><<<grid, (kScanCols / kScanThreadCols) * SPLIT, ScanShared<DKP>::kBytes, stream>>>(
+            q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status, segment_list, v_columns);
+    } else {
+        static OncePerDevice once;
+        allow_shared_memory(once, gdr_scan_kernel<DKP, SPLIT, false>, static_cast<int>(ScanShared<DKP>::kBytes));
+        gdr_scan_kernel<DKP, SPLIT, false><<<grid, (kScanCols / kScanThreadCols) * SPLIT, ScanShared<DKP>::kBytes, stream>>>(
+            q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status, segment_list, v_columns);
+    }
 }
 
 }  // namespace lb
@@ -536,6 +548,7 @@ int lb_gdr_conv_state(const void* proj, int proj_width, void* conv_state, const 
 }
 
 // segment_list (may be null): the portions to run, `segments` of them.  v_columns: the columns `v` has (0: dv).
+// beta null: the plain linear recurrence (no delta rule).
 int lb_gdr_scan(const float* q, const float* k, const float* g, const float* v, const float* beta, float* state, float* out,
                 const int* segment_start, const int* segment_length, const int* segment_slot, int segments, int heads, int groups, int dk, int dv,
                 int num_slots, int* status, cudaStream_t stream, const int* segment_list, int v_columns) {

@@ -26,18 +26,23 @@ __device__ __forceinline__ void warp_argmax(float& value, int& index) {
 //   only one, in groups of one); experts outside the best `group_keep` groups cannot be chosen;
 //   chosen[t, :] = the `top` eligible experts of largest s, in that order; weights[t, :] = their s (divided by their
 //   sum if `renormalize` is 1; the softmax over just the chosen s if it is 2), times `weight_scale`.
+//   `choice_bias` (may be null): experts (and groups) are ranked by s[e] + choice_bias[e]; the weights stay the s themselves.
+//   `extra` further rows of `router` after the experts' are gates of something every token runs: extra_out[t, x] =
+//   sigmoid(x_t . router[experts + x]), 32-bit like the scores.
 // Shared memory per warp: s[experts], candidates[experts], group score[group_count], and the token's row in 32-bit where it is staged.
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, int* __restrict__ chosen, float* __restrict__ weights,
                                  int tokens, int width, int experts, int top, int group_count, int group_keep, int score_kind, int renormalize,
-                                 float weight_scale, int row_floats, int group_floats, const float* __restrict__ bias, int block_per_token) {
+                                 float weight_scale, int row_floats, int group_floats, const float* __restrict__ bias, int block_per_token,
+                                 const float* __restrict__ choice_bias, int extra, float* __restrict__ extra_out) {
     extern __shared__ __align__(16) float shared[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int token = block_per_token ? blockIdx.x : blockIdx.x * warps + warp;
     if (token >= tokens) return;
     const int sharers = block_per_token ? warps : 1, share = block_per_token ? warp : 0;   // the logits of experts 4 (share + i sharers) .. + 3 are this warp's
-    float* scores = shared + static_cast<size_t>(block_per_token ? 0 : warp) * (2 * experts + group_floats + row_floats);   // a multiple of 4 floats per warp
-    float* candidates = scores + experts;
+    const int logits = experts + extra;   // rows of the router
+    float* scores = shared + static_cast<size_t>(block_per_token ? 0 : warp) * (experts + logits + group_floats + row_floats);   // a multiple of 4 floats per warp
+    float* candidates = scores + logits;
     float* group_score = candidates + experts;   // group_floats >= group_count of them
     float* x_s = group_score + group_floats;   // row_floats = width (rounded up to a multiple of 4) if the row is staged, else 0
     const T* row = x + static_cast<size_t>(token) * width;
@@ -51,14 +56,14 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
             for (int d = lane; d < width; d += 32) x_s[d] = to_float(row[d]);
             __syncwarp();
         }
-        for (int e0 = 4 * share; e0 < experts; e0 += 4 * sharers) {
+        for (int e0 = 4 * share; e0 < logits; e0 += 4 * sharers) {
             float dots[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 4
             for (int c = 4 * lane; c < width; c += 128) {   // sixteen loads of the router's rows on their way at a time
                 const float4 xv = *reinterpret_cast<const float4*>(x_s + c);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
-                    const float4 w = *reinterpret_cast<const float4*>(router + static_cast<size_t>(e0 + r < experts ? e0 + r : e0) * width + c);
+                    const float4 w = *reinterpret_cast<const float4*>(router + static_cast<size_t>(e0 + r < logits ? e0 + r : e0) * width + c);
                     dots[r] += xv.x * w.x;
                     dots[r] += xv.y * w.y;
                     dots[r] += xv.z * w.z;
@@ -68,11 +73,11 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 const float dot = warp_sum(dots[r]);
-                if (lane == 0 && e0 + r < experts) scores[e0 + r] = dot;
+                if (lane == 0 && e0 + r < logits) scores[e0 + r] = dot;
             }
         }
     } else {
-        for (int e = share; e < experts; e += sharers) {
+        for (int e = share; e < logits; e += sharers) {
             const float* w = router + static_cast<size_t>(e) * width;
             float dot = 0.0f;
             for (int d = lane; d < width; d += 32) dot += to_float(row[d]) * w[d];
@@ -85,6 +90,7 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
         if (warp != 0) return;
     }
     __syncwarp();
+    for (int x = lane; x < extra; x += 32) extra_out[static_cast<size_t>(token) * extra + x] = 1.0f / (1.0f + expf(-scores[experts + x]));
     if (bias != nullptr) {
         for (int e = lane; e < experts; e += 32) scores[e] += bias[e];
         __syncwarp();
@@ -107,7 +113,7 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
     for (int group = lane; group < group_count; group += 32) {
         float first = -INFINITY, second = -INFINITY;
         for (int m = 0; m < members; ++m) {
-            const float s = scores[group * members + m];
+            const float s = scores[group * members + m] + (choice_bias != nullptr ? choice_bias[group * members + m] : 0.0f);
             if (s > first) {
                 second = first;
                 first = s;
@@ -131,7 +137,8 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
         }
         warp_argmax(best, best_group);
         if (best_group == 0x7fffffff) break;
-        for (int m = lane; m < members; m += 32) candidates[best_group * members + m] = scores[best_group * members + m];
+        for (int m = lane; m < members; m += 32)
+            candidates[best_group * members + m] = scores[best_group * members + m] + (choice_bias != nullptr ? choice_bias[best_group * members + m] : 0.0f);
         if (lane == 0) group_score[best_group] = -INFINITY;
         __syncwarp();
     }
@@ -148,6 +155,7 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
         }
         warp_argmax(best, best_expert);
         if (best_expert == 0x7fffffff) best_expert = 0, best = 0.0f;   // fewer eligible experts than `top`: a weight of zero
+        else if (choice_bias != nullptr) best = scores[best_expert];   // ranked with the bias, weighed without it
         total += best;
         if (lane == 0) {
             chosen[static_cast<size_t>(token) * top + round] = best_expert;
@@ -186,7 +194,13 @@ __device__ __forceinline__ float moe_hidden(float gate, float up, int activation
     return round_to<T>(round_to<T>(moe_activate(round_to<T>(gate), activation)) * round_to<T>(up));
 }
 
-// One block per (token, chosen expert) pair p: hidden = act(W_gate[e] x) * (W_up[e] x), rounded to T; out[p] = W_down[e] hidden
+// The hidden value of an expert without a gate, act(W_up x), from its 32-bit sum: activated in 32-bit, rounded once.
+template <typename T>
+__device__ __forceinline__ float moe_plain_hidden(float up, int activation) {
+    return round_to<T>(moe_activate(up, activation));
+}
+
+// One block per (token, chosen expert) pair p (`gate` null: experts without a gate, hidden = act(W_up[e] x)): hidden = act(W_gate[e] x) * (W_up[e] x), rounded to T; out[p] = W_down[e] hidden
 // in 32-bit.  A warp per output row, lanes along the row, sums in lane order then over the warp.
 //   gate, up [experts, ff, width];  down [experts, width, ff];  out [pairs, width] (32-bit)
 template <typename T>
@@ -207,19 +221,19 @@ __global__ void moe_expert_stream_kernel(const T* __restrict__ x, const T* __res
     }
     for (int d = threadIdx.x; d < width; d += blockDim.x) x_s[d] = to_float(x[static_cast<size_t>(token) * width + d]);
     __syncthreads();
-    const T* gate_rows = gate + static_cast<size_t>(expert) * ff * width;
     const T* up_rows = up + static_cast<size_t>(expert) * ff * width;
+    const T* gate_rows = gate != nullptr ? gate + static_cast<size_t>(expert) * ff * width : up_rows;
     for (int f = warp; f < ff; f += warps) {
         const T* g_row = gate_rows + static_cast<size_t>(f) * width;
         const T* u_row = up_rows + static_cast<size_t>(f) * width;
         float g = 0.0f, u = 0.0f;
         for (int d = lane; d < width; d += 32) {
-            g += x_s[d] * to_float(g_row[d]);
+            if (gate != nullptr) g += x_s[d] * to_float(g_row[d]);
             u += x_s[d] * to_float(u_row[d]);
         }
         g = warp_sum(g);
         u = warp_sum(u);
-        if (lane == 0) hidden[f] = moe_hidden<T>(g, u, activation, limit);
+        if (lane == 0) hidden[f] = gate != nullptr ? moe_hidden<T>(g, u, activation, limit) : moe_plain_hidden<T>(u, activation);
     }
     __syncthreads();
     const T* down_rows = down + static_cast<size_t>(expert) * width * ff;
@@ -248,6 +262,26 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, const f
     }
 }
 
+// residual[t, :] += sum_k weights[t, k] * expert_out[t * top + k, :] + every_gate[t] * every[t, :] on the 32-bit residual stream:
+// the routed experts' weighted sum (in the order of k) and what every token runs besides (`every`, may be null; `every_gate`
+// one 32-bit number per token, null: 1), added in 32-bit without a rounding in between.
+template <typename T>
+__global__ void moe_combine_add_kernel(const float* __restrict__ expert_out, const float* __restrict__ weights, const int* __restrict__ chosen, int experts,
+                                       const T* __restrict__ every, const float* __restrict__ every_gate, int gate_stride, float* __restrict__ residual,
+                                       int top, int width) {
+    const int token = blockIdx.x;
+    const float gate = every_gate != nullptr ? every_gate[static_cast<size_t>(token) * gate_stride] : 1.0f;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        float sum = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            const int expert = chosen[static_cast<size_t>(token) * top + k];
+            if (expert < 0 || expert >= experts) continue;
+            sum += weights[static_cast<size_t>(token) * top + k] * expert_out[(static_cast<size_t>(token) * top + k) * width + d];
+        }
+        if (every != nullptr) sum += gate * to_float(every[static_cast<size_t>(token) * width + d]);
+        residual[static_cast<size_t>(token) * width + d] += sum;
+    }
+}
 
 // ---------------------------------------------------------------- few tokens: 16-byte loads, many blocks
 // The same two products with the rows of an expert's matrices shared out over blocks: grid (pairs, row slices),
@@ -293,7 +327,7 @@ __device__ __forceinline__ void four_dots(const float* __restrict__ x_s, const T
     for (int r = 0; r < 4; ++r) sums[r] = warp_sum(sums[r]);
 }
 
-// hidden[pair, f] = T(act(gate[e][f] . x) * (up[e][f] . x)) for the block's slice of f.
+// hidden[pair, f] = T(act(gate[e][f] . x) * (up[e][f] . x)) for the block's slice of f (`gate` null: T(act(up[e][f] . x))).
 template <typename T>
 __global__ void __launch_bounds__(32 * kStreamWarps)
 moe_gate_up_stream_kernel(const T* __restrict__ x, const T* __restrict__ gate, const T* __restrict__ up, const int* __restrict__ chosen,
@@ -308,8 +342,8 @@ moe_gate_up_stream_kernel(const T* __restrict__ x, const T* __restrict__ gate, c
     }
     for (int d = threadIdx.x; d < width; d += blockDim.x) x_s[d] = to_float(x[static_cast<size_t>(token) * width + d]);
     __syncthreads();
-    const T* gate_rows = gate + static_cast<size_t>(expert) * ff * width;
     const T* up_rows = up + static_cast<size_t>(expert) * ff * width;
+    const T* gate_rows = gate != nullptr ? gate + static_cast<size_t>(expert) * ff * width : up_rows;
     for (int f0 = first; f0 < min(ff, first + kStreamRowsPerWarp); f0 += 4) {
         const T* g_rows[4];
         const T* u_rows[4];
@@ -319,13 +353,13 @@ moe_gate_up_stream_kernel(const T* __restrict__ x, const T* __restrict__ gate, c
             g_rows[r] = gate_rows + static_cast<size_t>(f) * width;
             u_rows[r] = up_rows + static_cast<size_t>(f) * width;
         }
-        float g[4], u[4];
-        four_dots<T>(x_s, g_rows, width, lane, g);
+        float g[4] = {0.0f, 0.0f, 0.0f, 0.0f}, u[4];
+        if (gate != nullptr) four_dots<T>(x_s, g_rows, width, lane, g);
         four_dots<T>(x_s, u_rows, width, lane, u);
         if (lane < 4 && f0 + lane < ff) {
             const float gv = lane == 0 ? g[0] : lane == 1 ? g[1] : lane == 2 ? g[2] : g[3];
             const float uv = lane == 0 ? u[0] : lane == 1 ? u[1] : lane == 2 ? u[2] : u[3];
-            hidden[static_cast<size_t>(pair) * ff + f0 + lane] = from_float<T>(moe_hidden<T>(gv, uv, activation, limit));
+            hidden[static_cast<size_t>(pair) * ff + f0 + lane] = from_float<T>(gate != nullptr ? moe_hidden<T>(gv, uv, activation, limit) : moe_plain_hidden<T>(uv, activation));
         }
     }
 }
@@ -406,14 +440,16 @@ constexpr int kGroupedM = 64, kGroupedN = 64, kGroupedK = 32, kGroupedPitch = kG
 
 // One tile of 64 sorted pairs of one expert times 64 output columns, K in steps of 32 through two stages of
 // cp.async.  grid (tiles at most, column tiles); four warps of 16 rows each.
-//   GATED:  A = x rows gathered by the pairs' tokens [.., K = width], B = gate[e] and up[e] [N = ff][K];
+//   MODE 1 (gated):  A = x rows gathered by the pairs' tokens [.., K = width], B = gate[e] and up[e] [N = ff][K];
 //           hidden[place, n] = T(act(A . gate[n]) * (A . up[n]))
-//   else:   A = hidden[place] [K = ff], B = down[e] [N = width][K];   out[pair, n] = A . down[n]  (32-bit)
-template <bool GATED>
+//   MODE 2 (no gate):  A as above, B = up[e];   hidden[place, n] = T(act(A . up[n]))
+//   MODE 0 (down):   A = hidden[place] [K = ff], B = down[e] [N = width][K];   out[pair, n] = A . down[n]  (32-bit)
+template <int MODE>
 __global__ void __launch_bounds__(128)
 moe_grouped_kernel(const __nv_bfloat16* __restrict__ a_base, const __nv_bfloat16* __restrict__ b_first, const __nv_bfloat16* __restrict__ b_second,
                    const int* __restrict__ offsets, const int* __restrict__ sorted, __nv_bfloat16* __restrict__ hidden_out, float* __restrict__ pair_out,
                    int experts, int top, int n_total, int k_total, int activation, float limit) {
+    constexpr bool GATED = MODE == 1, UP = MODE != 0;   // UP: rows gathered by token, hidden values out
     __shared__ __align__(16) __nv_bfloat16 a_s[2][kGroupedM][kGroupedPitch];
     __shared__ __align__(16) __nv_bfloat16 b_s[GATED ? 2 : 1][2][kGroupedN][kGroupedPitch];
     __shared__ int row_source[kGroupedM];   // GATED: the token of the row's pair; else: the pair itself; -1 past the expert's pairs
@@ -438,7 +474,7 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ a_base, const __nv_bfloat16
     if (expert < 0) return;
     if (threadIdx.x < kGroupedM) {
         const int pair = static_cast<int>(threadIdx.x) < rows ? sorted[first + threadIdx.x] : -1;
-        row_source[threadIdx.x] = pair < 0 ? -1 : (GATED ? pair / top : pair);
+        row_source[threadIdx.x] = pair < 0 ? -1 : (UP ? pair / top : pair);
     }
     __syncthreads();
     const int n0 = blockIdx.y * kGroupedN;
@@ -451,7 +487,7 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ a_base, const __nv_bfloat16
             const int row = index >> 2, chunk = index & 3, k = k0 + 8 * chunk;
             const bool in_k = k < k_total;
             const int source = row_source[row];
-            const size_t a_row = GATED ? static_cast<size_t>(source < 0 ? 0 : source) : static_cast<size_t>(first + row);
+            const size_t a_row = UP ? static_cast<size_t>(source < 0 ? 0 : source) : static_cast<size_t>(first + row);
             moe_copy_16(&a_s[stage][row][8 * chunk], a_base + a_row * k_total + k, in_k && source >= 0);
             const bool in_n = n0 + row < n_total;
             const size_t b_row = b_expert + static_cast<size_t>(in_n ? n0 + row : 0) * k_total + k;
@@ -512,6 +548,9 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ a_base, const __nv_bfloat16
                     using T = __nv_bfloat16;
                     const float gate_value = acc[0][j][2 * half + e], up_value = acc[1][j][2 * half + e];
                     hidden_out[static_cast<size_t>(first + row) * n_total + n] = from_float<T>(moe_hidden<T>(gate_value, up_value, activation, limit));
+                } else if constexpr (UP) {
+                    using T = __nv_bfloat16;
+                    hidden_out[static_cast<size_t>(first + row) * n_total + n] = from_float<T>(moe_plain_hidden<T>(acc[0][j][2 * half + e], activation));
                 } else {
                     pair_out[static_cast<size_t>(row_source[row]) * n_total + n] = acc[0][j][2 * half + e];
                 }
@@ -525,24 +564,27 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ a_base, const __nv_bfloat16
 extern "C" {
 
 int lb_moe_route(const void* x, const float* router, int* chosen, float* weights, int tokens, int width, int experts, int top, int group_count,
-                 int group_keep, int score_kind, int renormalize, float weight_scale, int dtype, cudaStream_t stream, const float* bias) {
+                 int group_keep, int score_kind, int renormalize, float weight_scale, int dtype, cudaStream_t stream, const float* bias,
+                 const float* choice_bias, int extra, float* extra_out) {
+    // `router` has experts + extra rows; extra_out [tokens, extra] (see the kernel).
     if (tokens == 0) return 0;
     if (experts < 1 || top < 1 || top > experts || group_count < 1 || experts % group_count != 0 || group_keep < 1 || group_keep > group_count) return -2;
+    if (extra < 0 || (extra > 0 && extra_out == nullptr)) return -2;
     constexpr int kWarps = 4;
     // A warp's scratch: scores, candidates, group scores (padded so that the staged row starts on 16 bytes), and the row.
-    const int scratch = (2 * experts + group_count + 3) / 4 * 4;
+    const int scratch = (2 * experts + extra + group_count + 3) / 4 * 4;
     if (static_cast<size_t>(kWarps) * scratch * sizeof(float) > 48 * 1024) return -2;
     int row_floats = width % 4 == 0 ? width : 0;   // rows of 16-byte multiples are staged and read 16 bytes a lane
     if (static_cast<size_t>(kWarps) * (scratch + row_floats) * sizeof(float) > 160 * 1024) row_floats = 0;
     const size_t shared = static_cast<size_t>(kWarps) * (scratch + row_floats) * sizeof(float);
     const int block_per_token = tokens <= 512 ? 1 : 0;   // few tokens: a block's warps share out a token's experts
-    const int padded_groups = scratch - 2 * experts;   // the kernel lays the three arrays out by these counts
+    const int padded_groups = scratch - 2 * experts - extra;   // the kernel lays the three arrays out by these counts
     LB_DISPATCH_DTYPE(dtype, {
         auto kernel = lb::moe_route_kernel<T>;
         if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
         kernel<<<block_per_token ? tokens : (tokens + kWarps - 1) / kWarps, 32 * kWarps, shared, stream>>>(
             static_cast<const T*>(x), router, chosen, weights, tokens, width, experts, top, group_count, group_keep, score_kind, renormalize, weight_scale,
-            row_floats, padded_groups, bias, block_per_token);
+            row_floats, padded_groups, bias, block_per_token, choice_bias, extra, extra_out);
     })
     return LB_LAUNCH_RESULT();
 }
@@ -566,6 +608,16 @@ int lb_moe_combine(const float* expert_out, const float* weights, const int* cho
     if (tokens == 0) return 0;
     LB_DISPATCH_DTYPE(dtype, {
         lb::moe_combine_kernel<T><<<tokens, 256, 0, stream>>>(expert_out, weights, chosen, experts, static_cast<T*>(out), top, width);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_moe_combine_add(const float* expert_out, const float* weights, const int* chosen, int experts, const void* every, const float* every_gate,
+                       int gate_stride, float* residual, int tokens, int top, int width, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::moe_combine_add_kernel<T><<<tokens, 256, 0, stream>>>(expert_out, weights, chosen, experts, static_cast<const T*>(every), every_gate, gate_stride,
+                                                                   residual, top, width);
     })
     return LB_LAUNCH_RESULT();
 }
@@ -600,10 +652,15 @@ int lb_moe_experts_grouped(const void* x, const void* gate, const void* up, cons
     lb::moe_sort_kernel<<<1, 1024, 2 * experts * sizeof(int), stream>>>(chosen, pairs, experts, offsets, sorted);
     const int tiles = (pairs + lb::kGroupedM - 1) / lb::kGroupedM + experts;   // no fewer than the experts' tiles together
     const auto* x16 = static_cast<const __nv_bfloat16*>(x);
-    lb::moe_grouped_kernel<true><<<dim3(tiles, (ff + lb::kGroupedN - 1) / lb::kGroupedN), 128, 0, stream>>>(
-        x16, static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), offsets, sorted, static_cast<__nv_bfloat16*>(hidden), nullptr, experts,
-        top, ff, width, activation, limit);
-    lb::moe_grouped_kernel<false><<<dim3(tiles, (width + lb::kGroupedN - 1) / lb::kGroupedN), 128, 0, stream>>>(
+    if (gate != nullptr)
+        lb::moe_grouped_kernel<1><<<dim3(tiles, (ff + lb::kGroupedN - 1) / lb::kGroupedN), 128, 0, stream>>>(
+            x16, static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), offsets, sorted, static_cast<__nv_bfloat16*>(hidden), nullptr, experts,
+            top, ff, width, activation, limit);
+    else
+        lb::moe_grouped_kernel<2><<<dim3(tiles, (ff + lb::kGroupedN - 1) / lb::kGroupedN), 128, 0, stream>>>(
+            x16, static_cast<const __nv_bfloat16*>(up), nullptr, offsets, sorted, static_cast<__nv_bfloat16*>(hidden), nullptr, experts, top, ff, width, activation,
+            limit);
+    lb::moe_grouped_kernel<0><<<dim3(tiles, (width + lb::kGroupedN - 1) / lb::kGroupedN), 128, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(hidden), static_cast<const __nv_bfloat16*>(down), nullptr, offsets, sorted, nullptr, out, experts, top, width, ff, activation, limit);
     return LB_LAUNCH_RESULT();
 }

@@ -1176,59 +1176,72 @@ _ROUTER_SCORES = {"sigmoid": 0, "softmax": 1, "logits": 2}
 
 def moe_route(x: torch.Tensor, router: torch.Tensor, *, top: int, group_count: int = 1, group_keep: int = 1, score: str = "sigmoid",
               renormalize: bool = False, weight_scale: float = 1.0, bias: torch.Tensor | None = None,
-              chosen_softmax: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+              chosen_softmax: bool = False, choice_bias: torch.Tensor | None = None, extra: int = 0) -> tuple:
     """Chooses ``top`` experts per token: 32-bit router logits ``x @ router.T``, scores (``"sigmoid"`` or
     ``"softmax"``), only experts of the ``group_keep`` best of ``group_count`` groups of neighbours eligible
     (a group's score: the sum of its two largest scores).  Returns ``(chosen int32 [tokens, top], weights
     float32 [tokens, top])``, the weights being the chosen scores (over their sum if ``renormalize``; their softmax
     if ``chosen_softmax``) times ``weight_scale``.  ``bias`` (32-bit, one per expert) is added to the logits;
-    ``score="logits"`` ranks by the logits themselves."""
+    ``score="logits"`` ranks by the logits themselves.  ``choice_bias`` (32-bit, one per expert) is added to the scores where
+    experts are ranked, not where they weigh.  ``extra``: the router's last ``extra`` rows are no experts but gates; the
+    sigmoids of their logits are returned as a third value, float32 ``[tokens, extra]``."""
     _check(x, "x")
     _check(router, "router", torch.float32)
     if bias is not None:
         _check(bias, "bias", torch.float32)
-        if bias.numel() != router.shape[0]:
+        if bias.numel() != router.shape[0] - extra:
             raise KernelError("moe_route: the bias must have one element per expert")
     if score not in _ROUTER_SCORES:
         raise KernelError(f"moe_route: unknown score {score!r}; known: {sorted(_ROUTER_SCORES)}")
     tokens, width = x.shape
-    experts = router.shape[0]
+    if extra < 0 or extra >= router.shape[0]:
+        raise KernelError("moe_route: the router must have rows for the experts besides the extra ones")
+    experts = router.shape[0] - extra
     if router.shape[1] != width:
         raise KernelError("moe_route: the router's width is not x's")
+    if choice_bias is not None:
+        _check(choice_bias, "choice_bias", torch.float32)
+        if choice_bias.numel() != experts:
+            raise KernelError("moe_route: the choice bias must have one element per expert")
     if not (1 <= top <= experts and group_count >= 1 and experts % group_count == 0 and 1 <= group_keep <= group_count):
         raise KernelError(f"moe_route: top {top} of {experts} experts in {group_count} groups of which {group_keep} are kept is not a valid choice")
-    if 4 * (2 * experts + group_count) * 4 > 48 * 1024:
+    if 4 * (2 * experts + extra + group_count) * 4 > 48 * 1024:
         raise KernelError(f"moe_route: {experts} experts exceed the kernel's shared memory")
     chosen = torch.empty(tokens, top, dtype=torch.int32, device=x.device)
     weights = torch.empty(tokens, top, dtype=torch.float32, device=x.device)
+    extra_out = torch.empty(tokens, extra, dtype=torch.float32, device=x.device) if extra else None
     code = _lib().lb_moe_route(_ptr(x), _ptr(router), _ptr(chosen), _ptr(weights), c_int(tokens), c_int(width), c_int(experts), c_int(top), c_int(group_count),
                                c_int(group_keep), c_int(_ROUTER_SCORES[score]), c_int(2 if chosen_softmax else 1 if renormalize else 0), c_float(weight_scale),
-                               c_int(dtype_code(x.dtype)), _stream(), _ptr(bias))
+                               c_int(dtype_code(x.dtype)), _stream(), _ptr(bias), _ptr(choice_bias), c_int(extra), _ptr(extra_out))
     _done(code, "moe_route")
+    if extra:
+        return chosen, weights, extra_out
     return chosen, weights
 
 
 MOE_STREAM_MAX_PAIRS = 32  # up to this many (token, expert) pairs each pair streams its expert's weights; more are grouped by expert (measured: 24 pairs 30 % faster streamed, 48 pairs as fast either way)
 
 
-def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
+def moe_experts(x: torch.Tensor, gate: "torch.Tensor | None", up: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
                 activation: str = "silu", path: str | None = None, limit: float = 0.0, combine: bool = True) -> "torch.Tensor | ExpertSum":
     """``out[t] = sum_k weights[t, k] * down[e] (act(gate[e] x[t]) * (up[e] x[t]))`` with ``e = chosen[t, k]``;
     ``gate`` and ``up`` are ``[experts, ff, width]``, ``down`` ``[experts, width, ff]``.  The weighted sum is
     32-bit, in the order of ``k``; a pair whose expert is no expert counts nothing.  ``path`` forces one of the
     three ways the pairs' products are computed (``"grouped"``, ``"stream"``, ``"plain"``); left out, the sizes
-    choose.  ``combine=False`` leaves the weighted sum to the consumer (an :class:`ExpertSum`)."""
+    choose.  ``combine=False`` leaves the weighted sum to the consumer (an :class:`ExpertSum`).  ``gate=None``: experts
+    without a gate, ``down[e] act(up[e] x[t])`` (the activation in 32-bit on the 32-bit sums, rounded once)."""
     _check(x, "x")
     for name, tensor in (("gate", gate), ("up", up), ("down", down)):
-        _check(tensor, name, x.dtype)
+        if tensor is not None:
+            _check(tensor, name, x.dtype)
     _check(chosen, "chosen", torch.int32)
     _check(weights, "weights", torch.float32)
     if activation not in _ACTIVATIONS:
         raise KernelError(f"unknown activation {activation!r}; known: {sorted(_ACTIVATIONS)}")
     tokens, width = x.shape
-    experts, ff = gate.shape[0], gate.shape[1]
+    experts, ff = up.shape[0], up.shape[1]
     top = chosen.shape[1]
-    if gate.shape != (experts, ff, width) or up.shape != gate.shape or down.shape != (experts, width, ff) or chosen.shape != (tokens, top) or weights.shape != chosen.shape:
+    if up.shape != (experts, ff, width) or (gate is not None and gate.shape != up.shape) or down.shape != (experts, width, ff) or chosen.shape != (tokens, top) or weights.shape != chosen.shape:
         raise KernelError("moe_experts: shapes of x, the experts' weights, chosen and weights do not agree")
     if (width + ff) * 4 > 200 * 1024:
         raise KernelError("moe_experts: width + ff exceed the kernel's shared memory")
@@ -1270,6 +1283,216 @@ def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: tor
                               c_int(dtype_code(x.dtype)), _stream())
     _done(code, "moe_combine")
     return out
+
+
+def moe_combine_add(routed: ExpertSum, residual: torch.Tensor, every: torch.Tensor | None = None, every_gate: torch.Tensor | None = None) -> None:
+    """``residual[t] += sum_k weights[t, k] * pair_out[t * top + k] + every_gate[t] * every[t]`` on the 32-bit residual stream, in
+    32-bit: the routed experts' weighted sum, what every token runs besides (``every``, optional, in the activation type) times
+    a 32-bit number per token (``every_gate`` ``[tokens, 1]`` or ``[tokens]``; left out: 1)."""
+    _check(residual, "residual", torch.float32)
+    for name, tensor, dtype in (("pair_out", routed.pair_out, torch.float32), ("weights", routed.weights, torch.float32), ("chosen", routed.chosen, torch.int32)):
+        _check(tensor, name, dtype)
+    tokens, top = routed.chosen.shape
+    width = routed.pair_out.shape[1]
+    if residual.shape != (tokens, width) or routed.pair_out.shape[0] != tokens * top or routed.weights.shape != routed.chosen.shape:
+        raise KernelError("moe_combine_add: the experts' outputs, weights and choices do not fit the residual stream")
+    if every is not None:
+        _check(every, "every", routed.dtype)
+        if every.shape != residual.shape:
+            raise KernelError("moe_combine_add: `every` must have the residual stream's shape")
+    if every_gate is not None:
+        _check(every_gate, "every_gate", torch.float32)
+        if every is None or every_gate.numel() != tokens:
+            raise KernelError("moe_combine_add: the gate needs `every` and one element per token")
+    code = _lib().lb_moe_combine_add(_ptr(routed.pair_out), _ptr(routed.weights), _ptr(routed.chosen), c_int(routed.experts), _ptr(every), _ptr(every_gate), c_int(1),
+                                     _ptr(residual), c_int(tokens), c_int(top), c_int(width), c_int(dtype_code(routed.dtype)), _stream())
+    _done(code, "moe_combine_add")
+
+
+# ----------------------------------------------------------------------- branch norms
+def branch_norms_accumulate(residual: torch.Tensor, terms: list, eps: float) -> None:
+    """``residual += sum_i scale_i * rms_norm(tensor_i) * weight_i`` on the 32-bit residual stream, all in 32-bit; ``terms`` holds
+    one or two ``(tensor, weight, scale)``: the outputs of mixers side by side, each normed over the model's width."""
+    _check(residual, "residual", torch.float32)
+    if not 1 <= len(terms) <= 2:
+        raise KernelError("branch_norms_accumulate: one or two terms")
+    first = terms[0][0]
+    for tensor, weight, _ in terms:
+        _check(tensor, "branch output", first.dtype)
+        _check(weight, "branch weight", torch.float32)
+        if tensor.shape != residual.shape or weight.numel() != residual.shape[1]:
+            raise KernelError("branch_norms_accumulate: a branch's output or weight does not fit the residual stream")
+    second = terms[1] if len(terms) == 2 else (None, None, 0.0)
+    code = _lib().lb_branch_norms_accumulate(_ptr(residual), _ptr(first), _ptr(terms[0][1]), c_float(terms[0][2]), _ptr(second[0]), _ptr(second[1]), c_float(second[2]),
+                                             c_int(residual.shape[0]), c_int(residual.shape[1]), c_float(eps), c_int(dtype_code(first.dtype)), _stream())
+    _done(code, "branch_norms_accumulate")
+
+
+# ---------------------------------------------------------------------- linear attention
+def linear_attention(proj: torch.Tensor, matrix_state: torch.Tensor, *, num_heads: int, key_dim: int, value_dim: int, decay_logits: torch.Tensor | None = None,
+                     decay_bias: torch.Tensor | None = None, fixed_decay: torch.Tensor | None = None, tau: float = 1.0, query_scale: float = 1.0,
+                     key_scale: float = 1.0, norm_weight: torch.Tensor, norm_eps: float, gate_offset: int, gate_activation: str = "silu",
+                     segment_start: torch.Tensor, segment_length: torch.Tensor, segment_slot: torch.Tensor, segments: int, status: torch.Tensor) -> torch.Tensor:
+    """Linear attention ``S_t = diag(a_t) S_(t-1) + k_t v_t^T; o_t = S_t^T q_t`` over the step's portions, from each request's state
+    slot and back into it, then the per-head RMS norm of the read-out (times ``norm_weight``) times the gate.
+
+    ``proj`` ``[tokens, >= gate_offset + heads * value_dim]`` holds per token q (``heads x key_dim``), k (the same), v
+    (``heads x value_dim``) and, from column ``gate_offset`` on, the gate's logits.  The decay is ``fixed_decay`` (32-bit, one per
+    head) or ``sigmoid(decay_logits + decay_bias) ** (1 / tau)`` (``decay_logits`` ``[tokens, heads * key_dim]`` in the
+    activation type, the bias 32-bit).  ``matrix_state`` is ``[slots, heads, key_dim, value_dim]`` in 32-bit.  Returns
+    ``[tokens, heads * value_dim]`` in the activation type."""
+    _check(proj, "proj")
+    _check(matrix_state, "matrix_state", torch.float32)
+    _check(norm_weight, "norm_weight", torch.float32)
+    for name, tensor in (("segment_start", segment_start), ("segment_length", segment_length), ("segment_slot", segment_slot)):
+        _check(tensor, name, torch.int32)
+    if gate_activation not in ("sigmoid", "silu"):
+        raise KernelError(f"linear_attention: unknown gate activation {gate_activation!r}")
+    tokens = proj.shape[0]
+    if key_dim < 1 or key_dim > 256 or value_dim < 1 or num_heads < 1:
+        raise KernelError(f"linear_attention: {num_heads} heads with key size {key_dim} (at most 256) and value size {value_dim} are not supported")
+    if gate_offset < 2 * num_heads * key_dim + num_heads * value_dim or proj.shape[1] < gate_offset + num_heads * value_dim:
+        raise KernelError("linear_attention: proj is too narrow for the head counts")
+    num_slots = matrix_state.shape[0]
+    if matrix_state.shape != (num_slots, num_heads, key_dim, value_dim) or norm_weight.numel() != value_dim:
+        raise KernelError("linear_attention: matrix_state must be [slots, heads, key_dim, value_dim] and norm_weight [value_dim]")
+    if (decay_logits is None) == (fixed_decay is None):
+        raise KernelError("linear_attention: the decay is either fixed per head or made from logits")
+    if decay_logits is not None:
+        if not decay_logits.is_cuda or decay_logits.dim() != 2 or decay_logits.stride(1) != 1 or decay_logits.dtype != proj.dtype or decay_logits.shape[0] != tokens \
+                or decay_logits.shape[1] < num_heads * key_dim:
+            raise KernelError("linear_attention: decay_logits must be [tokens, >= heads * key_dim] of proj's type with unit column stride")
+        if decay_bias is not None:
+            _check(decay_bias, "decay_bias", torch.float32)
+            if decay_bias.numel() != num_heads * key_dim:
+                raise KernelError("linear_attention: decay_bias must have heads * key_dim elements")
+        if tau <= 0.0:
+            raise KernelError("linear_attention: tau must be positive")
+    else:
+        _check(fixed_decay, "fixed_decay", torch.float32)
+        if fixed_decay.numel() != num_heads:
+            raise KernelError("linear_attention: fixed_decay must have one element per head")
+    device = proj.device
+    q = torch.empty(tokens, num_heads, key_dim, dtype=torch.float32, device=device)
+    k = torch.empty_like(q)
+    decay = torch.empty_like(q)
+    v = torch.empty(tokens, num_heads, value_dim, dtype=torch.float32, device=device)
+    lib = _lib()
+    code = lib.lb_linear_attention_prepare(_ptr(proj), c_int(proj.shape[1]), _ptr(decay_logits), c_int(decay_logits.stride(0) if decay_logits is not None else 0),
+                                           _ptr(decay_bias), _ptr(fixed_decay), c_float(1.0 / tau), c_float(query_scale), c_float(key_scale), _ptr(q), _ptr(k), _ptr(v),
+                                           _ptr(decay), c_int(tokens), c_int(num_heads), c_int(key_dim), c_int(value_dim), c_int(dtype_code(proj.dtype)), _stream())
+    _done(code, "linear_attention_prepare")
+    read_out = torch.empty(tokens, num_heads, value_dim, dtype=torch.float32, device=device)
+    # the scan of the gated delta rule without its correction (no beta)
+    code = lib.lb_gdr_scan(_ptr(q), _ptr(k), _ptr(decay), _ptr(v), _ptr(None), _ptr(matrix_state), _ptr(read_out), _ptr(segment_start), _ptr(segment_length),
+                           _ptr(segment_slot), c_int(segments), c_int(num_heads), c_int(num_heads), c_int(key_dim), c_int(value_dim), c_int(num_slots),
+                           _ptr(status), _stream(), _ptr(None), c_int(value_dim))
+    _done(code, "linear_attention_scan")
+    out = torch.empty(tokens, num_heads * value_dim, dtype=proj.dtype, device=device)
+    code = lib.lb_gdr_output(_ptr(read_out), _ptr(proj), c_int(proj.shape[1]), c_int(gate_offset), _ptr(norm_weight), _ptr(out), c_int(tokens),
+                             c_int(num_heads), c_int(value_dim), c_float(norm_eps), c_int(dtype_code(proj.dtype)), _stream(), c_int(1 if gate_activation == "silu" else 0))
+    _done(code, "linear_attention_output")
+    return out
+
+
+# ------------------------------------------------------------- pooled window attention
+def _check_pooled(k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor, groups: int, head_dim: int, value_dim: int, what: str) -> tuple[int, int, int]:
+    _check(k_pages, f"{what} key pages")
+    _check(v_pages, f"{what} value pages", k_pages.dtype)
+    _check(block_table, f"{what} block table", torch.int32)
+    pages, rows = k_pages.shape[0], k_pages.shape[1]
+    if k_pages.shape != (pages, rows, groups, head_dim) or v_pages.shape != (pages, groups, value_dim, rows) or block_table.dim() != 2:
+        raise KernelError(f"pooled attention: the {what} pages must be [pages, rows, groups, head_dim] and [pages, groups, value_dim, rows]")
+    return pages, rows, block_table.shape[1]
+
+
+def pooled_rewrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, *, qk_freq: torch.Tensor | None, rotary_dim: int,
+                   value_freq: torch.Tensor | None, interleaved: bool = False, positions: torch.Tensor, token_segment: torch.Tensor, block_table: torch.Tensor,
+                   num_heads: int, num_groups: int, head_dim: int, value_dim: int, write_kv: bool, status: torch.Tensor) -> None:
+    """Splits the rows of ``qkv`` (q ``heads x head_dim`` | k ``groups x head_dim`` | v ``groups x value_dim``; a column slice of a wider
+    product will do) into heads, rotates the first ``rotary_dim`` channels of q and k by the token's position (``qk_freq``: a 32-bit
+    frequency per pair) and, with ``value_freq`` (``value_dim / 2`` frequencies), all channels of v; q goes to ``q_out``, k and v
+    into the token's page row.  Angles, sines and cosines in 32-bit, one rounding."""
+    if not qkv.is_cuda or qkv.dim() != 2 or qkv.stride(1) != 1:
+        raise KernelError("pooled_rewrite: qkv must be a [tokens, .] CUDA tensor with unit column stride")
+    _check(q_out, "q_out", qkv.dtype)
+    pages, page_size, max_blocks = _check_pooled(k_pages, v_pages, block_table, num_groups, head_dim, value_dim, "token")
+    if k_pages.dtype != qkv.dtype:
+        raise KernelError("pooled_rewrite: the pages must have qkv's type")
+    tokens = qkv.shape[0]
+    if qkv.shape[1] < num_heads * head_dim + num_groups * (head_dim + value_dim) or q_out.shape != (tokens, num_heads * head_dim):
+        raise KernelError("pooled_rewrite: qkv or q_out does not fit the head counts")
+    if rotary_dim:
+        _check(qk_freq, "qk_freq", torch.float32)
+        if rotary_dim % 2 or rotary_dim > head_dim or qk_freq.numel() != rotary_dim // 2:
+            raise KernelError("pooled_rewrite: rotary_dim must be even, at most head_dim, with one frequency per pair")
+    if value_freq is not None:
+        _check(value_freq, "value_freq", torch.float32)
+        if value_dim % 2 or value_freq.numel() != value_dim // 2:
+            raise KernelError("pooled_rewrite: rotated values need an even value_dim and one frequency per pair")
+    for name, tensor in (("positions", positions), ("token_segment", token_segment)):
+        _check(tensor, name, torch.int32)
+    code = _lib().lb_pooled_rewrite(_ptr(qkv), c_int(qkv.stride(0)), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(qk_freq if rotary_dim else None), c_int(rotary_dim),
+                                    c_int(1 if interleaved else 0), _ptr(value_freq), c_int(1 if interleaved else 0), _ptr(positions), _ptr(token_segment),
+                                    _ptr(block_table), c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(value_dim), c_int(page_size),
+                                    c_int(pages), c_int(max_blocks), c_int(1 if write_kv else 0), c_int(dtype_code(qkv.dtype)), _ptr(status), _stream())
+    _done(code, "pooled_rewrite")
+
+
+def pooled_means(k_pages: torch.Tensor, v_pages: torch.Tensor, pool_k_pages: torch.Tensor, pool_v_pages: torch.Tensor, *, segment_length: torch.Tensor,
+                 segment_context: torch.Tensor, block_table: torch.Tensor, pool_table: torch.Tensor, segments: int, max_length: int, num_groups: int,
+                 head_dim: int, value_dim: int, pool: int, status: torch.Tensor) -> None:
+    """For every block of ``pool`` positions whose last position this step wrote: the mean of its keys and of its values as the
+    token pages hold them (32-bit sums in the order of the positions, one rounding) into row ``b % rows`` of the request's pooled
+    page ``pool_table[b / rows]``.  ``max_length``: the step's longest portion."""
+    pages, page_size, max_blocks = _check_pooled(k_pages, v_pages, block_table, num_groups, head_dim, value_dim, "token")
+    pool_pages, pool_rows, pool_blocks = _check_pooled(pool_k_pages, pool_v_pages, pool_table, num_groups, head_dim, value_dim, "pooled")
+    if pool_k_pages.dtype != k_pages.dtype or pool < 1:
+        raise KernelError("pooled_means: pages of one type and a positive block size")
+    for name, tensor in (("segment_length", segment_length), ("segment_context", segment_context)):
+        _check(tensor, name, torch.int32)
+    code = _lib().lb_pooled_means(_ptr(k_pages), _ptr(v_pages), _ptr(pool_k_pages), _ptr(pool_v_pages), _ptr(segment_length), _ptr(segment_context), _ptr(block_table),
+                                  _ptr(pool_table), c_int(segments), c_int(max_length), c_int(num_groups), c_int(head_dim), c_int(value_dim), c_int(page_size),
+                                  c_int(pages), c_int(max_blocks), c_int(pool_rows), c_int(pool_pages), c_int(pool_blocks), c_int(pool), c_int(dtype_code(k_pages.dtype)),
+                                  _ptr(status), _stream())
+    _done(code, "pooled_means")
+
+
+def pooled_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pool_k_pages: torch.Tensor | None, pool_v_pages: torch.Tensor | None,
+                           out: torch.Tensor, *, positions: torch.Tensor, token_segment: torch.Tensor, block_table: torch.Tensor, pool_table: torch.Tensor | None,
+                           num_heads: int, num_groups: int, head_dim: int, value_dim: int, scale: float, softcap: float, head_bias: torch.Tensor | None,
+                           window: int, pool: int, value_freq: torch.Tensor | None, interleaved: bool = False, status: torch.Tensor) -> None:
+    """Sigmoid-weighted attention of every token over the positions of its window and the pooled blocks wholly before it:
+    ``out[t, h] = sum_x sigmoid(cap(q . k_x * scale) + head_bias[h]) v_x`` (no normalisation), blocks first, then positions
+    upwards, all in 32-bit; with ``value_freq`` the sum is turned back by the token's position.  One block per token and head."""
+    _check(q, "q")
+    _check(out, "out", q.dtype)
+    pages, page_size, max_blocks = _check_pooled(k_pages, v_pages, block_table, num_groups, head_dim, value_dim, "token")
+    if pool:
+        pool_pages, pool_rows, pool_blocks = _check_pooled(pool_k_pages, pool_v_pages, pool_table, num_groups, head_dim, value_dim, "pooled")
+    else:
+        pool_pages, pool_rows, pool_blocks = 0, 1, 0
+    tokens = q.shape[0]
+    if q.shape != (tokens, num_heads * head_dim) or out.shape != (tokens, num_heads * value_dim) or k_pages.dtype != q.dtype or num_heads % num_groups:
+        raise KernelError("pooled_attention_plain: q, out or the pages do not fit the head counts")
+    if head_bias is not None:
+        _check(head_bias, "head_bias", torch.float32)
+        if head_bias.numel() != num_heads:
+            raise KernelError("pooled_attention_plain: one bias per head")
+    if value_freq is not None:
+        _check(value_freq, "value_freq", torch.float32)
+        if value_dim % 2 or value_freq.numel() != value_dim // 2:
+            raise KernelError("pooled_attention_plain: rotated values need an even value_dim and one frequency per pair")
+    if window < 1 or pool < 0 or value_dim > 512:
+        raise KernelError("pooled_attention_plain: a positive window, a block size that is not negative and values of at most 512 channels")
+    for name, tensor in (("positions", positions), ("token_segment", token_segment)):
+        _check(tensor, name, torch.int32)
+    code = _lib().lb_pooled_attention_plain(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(pool_k_pages if pool else None), _ptr(pool_v_pages if pool else None), _ptr(out),
+                                            _ptr(positions), _ptr(token_segment), _ptr(block_table), _ptr(pool_table if pool else None), c_int(tokens), c_int(num_heads),
+                                            c_int(num_groups), c_int(head_dim), c_int(value_dim), c_int(page_size), c_int(pages), c_int(max_blocks), c_int(pool_rows),
+                                            c_int(pool_pages), c_int(pool_blocks), c_float(scale), c_float(softcap), _ptr(head_bias), c_int(window), c_int(pool),
+                                            _ptr(value_freq), c_int(1 if interleaved else 0), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
+    _done(code, "pooled_attention_plain")
 
 
 # ------------------------------------------------------------------------------ sampling

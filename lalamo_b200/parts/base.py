@@ -104,6 +104,10 @@ class PagedKVNeed(CacheNeed):
     value_dim: int | None = None  # size of a value head; None: head_dim
     keep_first: int = 0  # under a window: the first positions of a request that are kept all the same
     values_in_keys: bool = False  # True: a row holds all a token leaves behind (values are read from the key rows); no value pages
+    # > 1: one row for every so many positions (means of blocks of positions, say): a page then has ceil(page_size / tokens_per_row) rows,
+    # row b of a request lies in the page of its block table's entry b // rows at row b % rows (a page that the request holds, since
+    # b // rows is no more than the block of position b * tokens_per_row)
+    tokens_per_row: int = 1
 
 
 @dataclass(frozen=True)

@@ -18,8 +18,9 @@ __all__ = ["Embedding", "Head", "LMHead", "StreamMix", "TokenEmbedding"]
 
 
 class Embedding(Part):
-    def forward(self, token_ids: torch.Tensor, tokens: int) -> torch.Tensor:
-        """The residual stream ``[tokens, model_dim]`` in 32-bit for these token ids."""
+    def forward(self, token_ids: torch.Tensor, tokens: int, positions: torch.Tensor | None = None) -> torch.Tensor:
+        """The residual stream ``[tokens, model_dim]`` in 32-bit for these token ids (at these positions, for an embedding
+        that looks at them)."""
         raise NotImplementedError
 
     def add_to(self, residual: torch.Tensor, token_ids: torch.Tensor) -> None:
@@ -38,14 +39,23 @@ class TokenEmbedding(Embedding):
     def __init__(self, spec: EmbeddingSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         super().__init__(spec, tensors, runtime)
         self.weight = runtime.matrix(tensors["weight"])
+        self.positions = runtime.matrix(tensors["positions"]) if spec.learned_positions else None
 
     @classmethod
     def tensor_decls(cls, spec: EmbeddingSpec) -> dict[str, TensorDecl]:
-        return {"weight": TensorDecl((spec.vocab_size, spec.model_dim))}
+        decls = {"weight": TensorDecl((spec.vocab_size, spec.model_dim))}
+        if spec.learned_positions:
+            decls["positions"] = TensorDecl((spec.learned_positions, spec.model_dim))
+        return decls
 
-    def forward(self, token_ids: torch.Tensor, tokens: int) -> torch.Tensor:
+    def forward(self, token_ids: torch.Tensor, tokens: int, positions: torch.Tensor | None = None) -> torch.Tensor:
         residual = self.runtime.empty(tokens, self.spec.model_dim, dtype=torch.float32)
         ops.embed(self.weight, token_ids, residual, self.spec.scale, self.runtime.status)
+        if self.positions is not None:
+            if positions is None:
+                raise ValueError("an embedding with learned position vectors needs the tokens' positions")
+            # the same gather with the positions as indices, unscaled and added; a position past the table is reported like a bad token id
+            ops.embed(self.positions, positions, residual, 1.0, self.runtime.status, accumulate=True)
         return residual
 
     def add_to(self, residual: torch.Tensor, token_ids: torch.Tensor) -> None:

@@ -113,7 +113,7 @@ class DecoderModel:
 
     def forward(self, step: StepInputs, caches: list[CacheView | None]) -> torch.Tensor:
         runtime = self.runtime
-        residual = self.embedding.forward(step.token_ids, step.tokens)
+        residual = self.embedding.forward(step.token_ids, step.tokens, step.positions)
         pending: torch.Tensor | None = None
         for position, entry in enumerate(self.plan.schedule):
             if entry.add_embedding:

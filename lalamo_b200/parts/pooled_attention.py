@@ -1,0 +1,106 @@
+"""Grouped attention with sigmoid weights under a sliding window, with one mean key and mean value for every whole block
+of positions before the window (see :class:`~lalamo_b200.config.plan.PooledWindowAttentionSpec`).
+
+The mixer holds two paged caches: the positions' keys and values under the window's retention rule (pages go back once
+the window and every unfinished block have passed them), and the blocks' means, one row per block, which are kept for
+good.  A step rotates q, k and v and writes the pages, computes the mean of every block it completed from the pages, and
+then attends: the visible blocks first, then the window's positions upwards, the weights ``sigmoid(cap(q . k scale) +
+bias_h)`` summed with the values in 32-bit without any normalisation; rotated values are turned back by the query's
+position at the end."""
+
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from .. import ops
+from ..config.plan import PooledWindowAttentionSpec, RopeSpec
+from .base import CacheNeed, CompositeNeed, CompositeView, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, register_part
+
+__all__ = ["PooledWindowAttention"]
+
+
+def _frequencies(dims: int, theta: float) -> torch.Tensor:
+    """``theta ** (-2m / dims)`` for the pairs ``m`` of ``dims`` channels, as the 32-bit table the kernels multiply positions with."""
+    channel = torch.arange(0, dims, 2, dtype=torch.float32)
+    return 1.0 / (torch.tensor(theta, dtype=torch.float32) ** (channel / dims))
+
+
+@register_part(PooledWindowAttentionSpec)
+class PooledWindowAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, spec: PooledWindowAttentionSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().__init__(spec, tensors, runtime)
+        if spec.num_heads % spec.num_groups:
+            raise ValueError(f"num_heads={spec.num_heads} is not a multiple of num_groups={spec.num_groups}")
+        if spec.window < 1 or spec.pool < 0 or spec.softcap < 0.0:
+            raise ValueError("the window must be positive, the block size and the cap not negative")
+        if spec.position is not None and not isinstance(spec.position, RopeSpec):
+            raise ValueError(f"pooled window attention applies rotary position encodings, not {type(spec.position).__name__}")
+        if spec.rotate_values and (spec.position is None or spec.value_dim % 2):
+            raise ValueError("rotated values need a rotary specification (for the base) and an even value_dim")
+        if spec.position is not None and spec.position.pairing not in ("half", "interleaved"):
+            raise ValueError(f"unknown rotary pairing {spec.position.pairing!r}; known: 'half', 'interleaved'")
+        if spec.position is not None and spec.position.scaling is not None:
+            raise ValueError("stretched frequencies are not supported here")
+        self.qkv = runtime.matrix(torch.cat([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]], dim=0))
+        self.out_proj = runtime.matrix(tensors["out_proj"])
+        self.head_bias = runtime.vector(tensors["head_bias"]) if spec.head_bias else None
+        self.rotary_dim = spec.position.rotary_dim if spec.position is not None else 0
+        self.interleaved = spec.position is not None and spec.position.pairing == "interleaved"
+        self.qk_freq = _frequencies(self.rotary_dim, spec.position.theta).to(runtime.device) if self.rotary_dim else None
+        self.value_freq = _frequencies(spec.value_dim, spec.position.theta).to(runtime.device) if spec.rotate_values else None
+        self.scale = spec.scale if spec.scale is not None else spec.head_dim ** -0.5
+
+    @classmethod
+    def tensor_decls(cls, spec: PooledWindowAttentionSpec) -> dict[str, TensorDecl]:
+        decls = {
+            "q_proj": TensorDecl((spec.num_heads * spec.head_dim, spec.model_dim)),
+            "k_proj": TensorDecl((spec.num_groups * spec.head_dim, spec.model_dim)),
+            "v_proj": TensorDecl((spec.num_groups * spec.value_dim, spec.model_dim)),
+            "out_proj": TensorDecl((spec.model_dim, spec.num_heads * spec.value_dim)),
+        }
+        if spec.head_bias:
+            decls["head_bias"] = TensorDecl((spec.num_heads,), role="vector")
+        return decls
+
+    def cache_need(self) -> CacheNeed | None:
+        spec = self.spec
+        # A block's mean is taken when its last position is written: until then its positions stay, also behind the window.
+        tokens = PagedKVNeed(num_groups=spec.num_groups, head_dim=spec.head_dim, window=max(spec.window, spec.pool), value_dim=spec.value_dim)
+        if not spec.pool:
+            return tokens
+        blocks = PagedKVNeed(num_groups=spec.num_groups, head_dim=spec.head_dim, window=None, value_dim=spec.value_dim, tokens_per_row=spec.pool)
+        return CompositeNeed((tokens, blocks))
+
+    can_accumulate = True
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: "PagedKVView | CompositeView", residual: torch.Tensor | None = None) -> torch.Tensor | None:  # type: ignore[override]
+        spec = self.spec
+        status = self.runtime.status
+        if spec.pool:
+            tokens_view, blocks_view = cache.views
+        else:
+            tokens_view, blocks_view = cache, None
+        qkv = ops.linear(x, self.qkv, status=status)
+        queries = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
+        shape = dict(num_heads=spec.num_heads, num_groups=spec.num_groups, head_dim=spec.head_dim, value_dim=spec.value_dim)
+        ops.pooled_rewrite(qkv, queries, tokens_view.k_pages, tokens_view.v_pages, qk_freq=self.qk_freq, rotary_dim=self.rotary_dim, value_freq=self.value_freq,
+                           interleaved=self.interleaved, positions=step.positions, token_segment=step.token_segment, block_table=tokens_view.block_table,
+                           write_kv=tokens_view.owns, status=status, **shape)
+        if blocks_view is not None and blocks_view.owns:
+            ops.pooled_means(tokens_view.k_pages, tokens_view.v_pages, blocks_view.k_pages, blocks_view.v_pages, segment_length=step.segment_length,
+                             segment_context=step.segment_context, block_table=tokens_view.block_table, pool_table=blocks_view.block_table,
+                             segments=step.segments, max_length=step.max_segment_length, num_groups=spec.num_groups, head_dim=spec.head_dim,
+                             value_dim=spec.value_dim, pool=spec.pool, status=status)
+        mixed = self.runtime.empty(step.tokens, spec.num_heads * spec.value_dim)
+        ops.pooled_attention_plain(queries, tokens_view.k_pages, tokens_view.v_pages, blocks_view.k_pages if blocks_view is not None else None,
+                                   blocks_view.v_pages if blocks_view is not None else None, mixed, positions=step.positions, token_segment=step.token_segment,
+                                   block_table=tokens_view.block_table, pool_table=blocks_view.block_table if blocks_view is not None else None,
+                                   scale=self.scale, softcap=spec.softcap, head_bias=self.head_bias, window=spec.window, pool=spec.pool,
+                                   value_freq=self.value_freq, interleaved=self.interleaved, status=status, **shape)
+        if residual is not None:
+            return ops.linear_accumulate(mixed, self.out_proj, residual, status=status)
+        return ops.linear(mixed, self.out_proj, status=status)
