@@ -308,7 +308,8 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
     layer (of a routed feed-forward the router and the experts a token uses), attention (a multiply-add per query, visible
     key and channel, for scores and for values, under the window if there is one), the delta rule's three passes over a
     head's state per token, and the read-out of the wanted rows."""
-    from lalamo_b200.config import AttentionSpec, DenseMLPSpec, GatedDeltaSpec, GatedMLPSpec, LatentAttentionSpec, ParallelMixerSpec, RoutedMLPSpec, ShortConvSpec
+    from lalamo_b200.config import (AttentionSpec, DenseMLPSpec, GatedDeltaSpec, GatedMLPSpec, LatentAttentionSpec, LinearAttentionSpec, ParallelMixerSpec,
+                                    PooledWindowAttentionSpec, RoutedMLPSpec, ShortConvSpec)
 
     def mixer_flops(spec) -> float:
         if isinstance(spec, ParallelMixerSpec):
@@ -333,6 +334,15 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
                 rows += spec.num_heads * (spec.key_dim if spec.decay_per_channel else 1) + spec.num_heads * spec.value_dim
             per_token = 2.0 * rows * spec.model_dim + 2.0 * inner * max(spec.decay_rank, spec.gate_rank) + 8.0 * spec.num_heads * spec.key_dim * spec.value_dim
             return per_token * tokens
+        if isinstance(spec, LinearAttentionSpec):
+            # q, k, v, gate and out projections, the decay's bottleneck, and two passes over a head's state per token
+            rows = 2 * spec.num_heads * spec.key_dim + 3 * spec.num_heads * spec.value_dim + spec.decay_rank
+            per_token = 2.0 * rows * spec.model_dim + 2.0 * spec.num_heads * spec.key_dim * spec.decay_rank + 4.0 * spec.num_heads * spec.key_dim * spec.value_dim
+            return per_token * tokens
+        if isinstance(spec, PooledWindowAttentionSpec):
+            rows = (spec.num_heads + spec.num_groups) * spec.head_dim + spec.num_groups * spec.value_dim + spec.num_heads * spec.value_dim
+            pairs = sum(min(position + 1, spec.window) + (max(0, position - spec.window + 1) // spec.pool if spec.pool else 0) for position in range(tokens))
+            return 2.0 * rows * spec.model_dim * tokens + 2.0 * spec.num_heads * (spec.head_dim + spec.value_dim) * pairs
         if isinstance(spec, ShortConvSpec):
             return 2.0 * 4 * spec.model_dim * spec.model_dim * tokens
         raise TypeError(f"no operation count for {type(spec).__name__}")
@@ -345,7 +355,7 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
         if isinstance(spec, DenseMLPSpec):
             return 2.0 * 2 * spec.model_dim * spec.hidden_dim * tokens
         if isinstance(spec, RoutedMLPSpec):
-            return 2.0 * (3 * spec.top * spec.hidden_dim + spec.num_experts) * spec.model_dim * tokens + ffn_flops(spec.shared)
+            return 2.0 * ((3 if spec.gated else 2) * spec.top * spec.hidden_dim + spec.num_experts) * spec.model_dim * tokens + ffn_flops(spec.shared)
         raise TypeError(f"no operation count for {type(spec).__name__}")
 
     total = 2.0 * plan.model_dim * plan.vocab_size * wanted_rows
@@ -362,7 +372,9 @@ def run_compare(arguments, peaks: dict, peak_source: str, families: tuple[str, .
     a prompt of 2,048 tokens in one step, and decode steps at batch 8 and 64 with 4,096 tokens behind every request.
     `--config tudulix-compare`: the same for the Tudulix shapes beside the Vuvulorn shapes.
     `--config vivulorn-compare`: the Vivulorn shapes beside the Tudulix shapes (attention, latent attention, a repeated stretch)
-    and the Vuvulorn shapes (the delta rule, dense feed-forwards)."""
+    and the Vuvulorn shapes (the delta rule, dense feed-forwards).
+    `--config zozenex-compare`: the Zozenex shapes beside the Vuvulorn shapes (attention under a window beside a recurrence with a
+    matrix state, routed experts) and the Tudulix shapes (every layer routed, a shared expert)."""
     import torch
 
     from lalamo_b200.config import config_from_dict
@@ -543,8 +555,8 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=500)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--compare-sizes", default="350m,1.2b", help="the sizes --config vuvulorn-compare, tudulix-compare and vivulorn-compare measure")
-    parser.add_argument("--config", default="lfm2-1.2b-decode", choices=["lfm2-1.2b-decode", "lfm2-350m-mixed", "lfm2-700m-long", "vuvulorn-compare", "tudulix-compare", "vivulorn-compare"],
+    parser.add_argument("--compare-sizes", default="350m,1.2b", help="the sizes --config vuvulorn-compare, tudulix-compare, vivulorn-compare and zozenex-compare measure")
+    parser.add_argument("--config", default="lfm2-1.2b-decode", choices=["lfm2-1.2b-decode", "lfm2-350m-mixed", "lfm2-700m-long", "vuvulorn-compare", "tudulix-compare", "vivulorn-compare", "zozenex-compare"],
                         help="lfm2-1.2b-decode (default): the decode step and its points; lfm2-350m-mixed: 64 requests with prompts of 128 to 2,048 "
                              "tokens and 256 new tokens through the scheduler; lfm2-700m-long: 16,384-token prompts at batch 1 and 8, then 512 decode steps")
     parser.add_argument("--batch", type=int, default=8)
@@ -587,6 +599,8 @@ def main() -> int:
         return run_compare(arguments, peaks, peak_source, families=("tudulix", "vuvulorn"))
     if arguments.config == "vivulorn-compare":
         return run_compare(arguments, peaks, peak_source, families=("vivulorn", "tudulix", "vuvulorn"))
+    if arguments.config == "zozenex-compare":
+        return run_compare(arguments, peaks, peak_source, families=("zozenex", "vuvulorn", "tudulix"))
     if arguments.requests:
         requests, prompt_length, new_tokens = (int(part) for part in arguments.requests.split(","))
         engine, config = build_engine(max_tokens=requests * (prompt_length + new_tokens + 64), max_requests=max(requests, 2), max_batch_tokens=2048)

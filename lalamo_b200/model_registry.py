@@ -169,6 +169,28 @@ def _vivulorn_shape(width: int, layers: int, heads: int, kv_heads: int, delta_he
     }
 
 
+def _zozenex_shape(width: int, layers: int, heads: int, kv_heads: int, linear_heads: int, linear_dim: int, linear_vdim: int, ff: int, experts: int, top: int) -> dict[str, Any]:
+    """A Zozenex shape for the random-weights mode: retention layers in turn with layers of two mixers side by side: sigmoid attention
+    with heads of 64 under a window of 1,024 tokens with one mean key and value for every 8 positions before it, and gated linear
+    attention; ``linear_heads`` heads of ``linear_dim`` x ``linear_vdim`` in both kinds of recurrence; every layer with ``top`` routed
+    experts of ``ff`` columns and a shared one of as many (no gates: two matrices each)."""
+    retention = {"heads": linear_heads, "dim": linear_dim, "vdim": linear_vdim, "decay": [1.0 - 2.0 ** (-5 - head) for head in range(linear_heads)]}
+    parallel = {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0, "mask": {"size": 1024, "pool": 8},
+                 "rot": {"dims": 64, "base": 1000000.0}},
+        "right": {"heads": linear_heads, "dim": linear_dim, "vdim": linear_vdim, "tau": 16.0, "rank": 64},
+    }
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 2.0}, "shared": {"ff": ff}}
+    return {
+        "architecture": "Zozenex",
+        "vocab": 65536,
+        "width": width,
+        "max_positions": 16384,
+        "norm": {"eps": 1e-5},
+        "layers": [{"type": "parallel" if index % 2 else "retention", "mixer": parallel if index % 2 else retention, "mlp": mlp} for index in range(layers)],
+    }
+
+
 # Shapes of the published checkpoints, and Vuvulorn shapes of the same widths and depths, for the random-weights mode
 # (no weights are downloaded).
 PRESETS: dict[str, dict[str, Any]] = {
@@ -183,4 +205,7 @@ PRESETS: dict[str, dict[str, Any]] = {
     # 14 layers of which two run twice (16 layer runs); the two projections of the plain feed-forward hold what the three of a gated one of 4,608 (8,192) columns hold
     "vivulorn-350m": _vivulorn_shape(1024, 14, 16, 4, 8, 64, 128, 6912, 256),
     "vivulorn-1.2b": _vivulorn_shape(2048, 14, 16, 4, 8, 128, 128, 12288, 256),
+    # 16 layers; 3 routed experts + the shared one hold in their two matrices each what the three of a gated feed-forward of 4,608 (8,192) columns hold
+    "zozenex-350m": _zozenex_shape(1024, 16, 16, 4, 8, 64, 128, 1728, 16, 3),
+    "zozenex-1.2b": _zozenex_shape(2048, 16, 16, 4, 8, 128, 128, 3072, 16, 3),
 }

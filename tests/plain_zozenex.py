@@ -117,13 +117,21 @@ def parallel_mixer(h: torch.Tensor, w: dict, cfg: dict, eps: float) -> torch.Ten
     return 0.5 * (rms_norm(left, w["left.out"], eps) + rms_norm(right, w["right.out"], eps))
 
 
-def routed_experts(h: torch.Tensor, w: dict, cfg: dict) -> torch.Tensor:
+def routed_experts(h: torch.Tensor, w: dict, cfg: dict, choice: torch.Tensor | None = None, slack: list | None = None) -> torch.Tensor:
+    """``choice`` ([tokens, top], optional): the experts to use instead of the ones this function would choose (for a comparison with
+    an implementation whose rounding may turn a close call); ``slack`` then receives, per token, by how much the best expert left
+    out beats the worst one taken in this function's own choice scores (not positive where the choice is the right one)."""
     experts, top, scale = cfg["router"]["experts"], cfg["router"]["top"], cfg["router"]["scale"]
     scores = torch.sigmoid(h @ w["router"].T)
-    choice = scores + w["correction"]
+    ranking = scores + w["correction"]
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        order = sorted(range(experts), key=lambda e: (-float(choice[t, e]), e))[:top]
+        order = sorted(range(experts), key=lambda e: (-float(ranking[t, e]), e))[:top]
+        if choice is not None:
+            order = [int(e) for e in choice[t]]
+            others = [float(ranking[t, e]) for e in range(experts) if e not in order]
+            if slack is not None and others:
+                slack.append(max(others) - min(float(ranking[t, e]) for e in order))
         for e in order:
             out[t] += scores[t, e] * scale * (gelu(h[t] @ w[f"e{e}.up"].T) @ w[f"e{e}.down"].T)
     if cfg.get("shared") is not None:
@@ -136,9 +144,11 @@ def sub(weights: dict, prefix: str) -> dict:
     return {name[len(prefix):]: tensor for name, tensor in weights.items() if name.startswith(prefix)}
 
 
-def forward(config: dict, weights: dict, tokens: list[int], layers_out: list | None = None) -> torch.Tensor:
+def forward(config: dict, weights: dict, tokens: list[int], layers_out: list | None = None, choices: dict | None = None,
+            slack: list | None = None) -> torch.Tensor:
     """Logits ``[tokens, vocab]`` of one request read whole; ``weights`` by checkpoint name, in float64.
-    ``layers_out`` (a list) receives the stream after every layer."""
+    ``layers_out`` (a list) receives the stream after every layer.  ``choices`` (layer -> [tokens, top]) and ``slack``: see
+    :func:`routed_experts`."""
     eps = config["norm"]["eps"]
     ids = torch.tensor(tokens, dtype=torch.long)
     x = weights["embed"][ids] + weights["pos"][: len(tokens)]
@@ -153,7 +163,7 @@ def forward(config: dict, weights: dict, tokens: list[int], layers_out: list | N
         else:
             raise ValueError(layer["type"])
         if layer.get("mlp") is not None:
-            x = x + routed_experts(rms_norm(x, w["norm2"], eps), sub(w, "mlp."), layer["mlp"])
+            x = x + routed_experts(rms_norm(x, w["norm2"], eps), sub(w, "mlp."), layer["mlp"], None if choices is None else choices[index], slack)
         if layers_out is not None:
             layers_out.append(x.clone())
     return rms_norm(x, weights["final.norm"], eps) @ weights["head"].T
