@@ -12,10 +12,10 @@
 // Four kernels: `pooled_rewrite` (rotation of q, k and v in 32-bit, one rounding, pages written), `pooled_means` (the mean
 // of every block that the step completes, from the pages, into the pooled pages), `pooled_attention_plain` (a block per token
 // and head, everything 32-bit: the 32-bit path and the reference for the tensor-core kernel) and `pooled_attention_mma`
-// (bfloat16 on mma.sync m16n8k16: a CTA takes 16 consecutive tokens of a portion and the query heads of one K/V head).
+// (bfloat16 on mma.sync m16n8k16: a CTA takes up to 64 consecutive tokens of a portion and up to four query heads of one K/V head).
 // Keys are summed in the order blocks 0, 1, ... then positions upwards, whatever the step's cutting.
 //
-// Token pages: keys [page][row][group][dk], values transposed [page][group][dv][row], `page_size` rows a page, found
+// Pages: a row holds all a position leaves behind, [page][row][group][key (dk) | value (dv)], `page_size` rows a page, found
 // through the token block table (block = position / page_size).  Pooled pages: the same with `pool_rows` rows a page,
 // block b in page pool_table[b / pool_rows], row b % pool_rows.
 #include "common.cuh"
@@ -60,7 +60,7 @@ __device__ __forceinline__ void rotation_pair(int c, int dims, int interleaved, 
 // grid (tokens): q [tokens, heads, dk] rotated into q_out; k rotated and v (rotated over all dv channels if v_freq is
 // given) into the token's page row.  qkv rows: q (heads x dk) | k (groups x dk) | v (groups x dv), row stride `stride`.
 template <typename T>
-__global__ void pooled_rewrite_kernel(const T* __restrict__ qkv, int stride, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+__global__ void pooled_rewrite_kernel(const T* __restrict__ qkv, int stride, T* __restrict__ q_out, T* __restrict__ pages,
                                       const float* __restrict__ qk_freq, int rot_dims, int qk_interleaved, const float* __restrict__ v_freq,
                                       int v_interleaved, const int* __restrict__ positions, const int* __restrict__ token_segment,
                                       const int* __restrict__ block_table, PooledLayout L, int heads, int write_kv, int* status) {
@@ -89,8 +89,8 @@ __global__ void pooled_rewrite_kernel(const T* __restrict__ qkv, int stride, T* 
                 report_error(status, kBadPage);
                 continue;
             }
-            const int kc = index - q_width;   // group * dk + c
-            k_pages[(static_cast<size_t>(page) * L.page_size + position % L.page_size) * k_width + kc] = from_float<T>(value);
+            const int group = (index - q_width) / L.dk;
+            pages[((static_cast<size_t>(page) * L.page_size + position % L.page_size) * L.groups + group) * (L.dk + L.dv) + c] = from_float<T>(value);
         }
     }
     if (!write_kv) return;
@@ -107,8 +107,7 @@ __global__ void pooled_rewrite_kernel(const T* __restrict__ qkv, int stride, T* 
             sincosf(p * v_freq[pair], &sine, &cosine);
             value = value * cosine + sign * to_float(row[q_width + k_width + index - c + partner]) * sine;
         }
-        // values transposed: [page][group][channel][row]
-        v_pages[(static_cast<size_t>(page) * v_width + index) * L.page_size + position % L.page_size] = from_float<T>(value);
+        pages[((static_cast<size_t>(page) * L.page_size + position % L.page_size) * L.groups + index / L.dv) * (L.dk + L.dv) + L.dk + c] = from_float<T>(value);
     }
 }
 
@@ -116,7 +115,7 @@ __global__ void pooled_rewrite_kernel(const T* __restrict__ qkv, int stride, T* 
 // position, gets the mean of its `pool` keys and values as the pages hold them (sums in 32-bit in the order of the
 // positions, divided by pool, rounded once).
 template <typename T>
-__global__ void pooled_means_kernel(const T* __restrict__ k_pages, const T* __restrict__ v_pages, T* __restrict__ pk_pages, T* __restrict__ pv_pages,
+__global__ void pooled_means_kernel(const T* __restrict__ pages, T* __restrict__ pooled_pages,
                                     const int* __restrict__ segment_length, const int* __restrict__ segment_context,
                                     const int* __restrict__ block_table, const int* __restrict__ pool_table, PooledLayout L, int pool, int* status) {
     const int segment = blockIdx.x;
@@ -132,9 +131,9 @@ __global__ void pooled_means_kernel(const T* __restrict__ k_pages, const T* __re
         return;
     }
     const int out_row = block_index % L.pool_rows;
-    const int k_width = L.groups * L.dk, v_width = L.groups * L.dv;
+    const int width = L.groups * (L.dk + L.dv);   // a row: every group's key and value
     const float inverse = 1.0f / static_cast<float>(pool);
-    for (int index = threadIdx.x; index < k_width + v_width; index += blockDim.x) {
+    for (int index = threadIdx.x; index < width; index += blockDim.x) {
         float sum = 0.0f;
         bool bad = false;
         for (int j = 0; j < pool; ++j) {
@@ -144,18 +143,13 @@ __global__ void pooled_means_kernel(const T* __restrict__ k_pages, const T* __re
                 bad = true;
                 break;
             }
-            const int r = position % L.page_size;
-            sum += index < k_width ? to_float(k_pages[(static_cast<size_t>(page) * L.page_size + r) * k_width + index])
-                                   : to_float(v_pages[(static_cast<size_t>(page) * v_width + (index - k_width)) * L.page_size + r]);
+            sum += to_float(pages[(static_cast<size_t>(page) * L.page_size + position % L.page_size) * width + index]);
         }
         if (bad) {
             report_error(status, kBadPage);
             continue;
         }
-        if (index < k_width)
-            pk_pages[(static_cast<size_t>(out_page) * L.pool_rows + out_row) * k_width + index] = from_float<T>(sum * inverse);
-        else
-            pv_pages[(static_cast<size_t>(out_page) * v_width + (index - k_width)) * L.pool_rows + out_row] = from_float<T>(sum * inverse);
+        pooled_pages[(static_cast<size_t>(out_page) * L.pool_rows + out_row) * width + index] = from_float<T>(sum * inverse);
     }
 }
 
@@ -171,8 +165,8 @@ constexpr int kPooledChunk = 128, kPooledThreads = 128, kPooledMaxDims = 4;   //
 // thread per item for the weights, a thread per channel for the sums (in item order).
 template <typename T>
 __global__ void __launch_bounds__(kPooledThreads)
-pooled_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages, const T* __restrict__ pk_pages,
-                              const T* __restrict__ pv_pages, T* __restrict__ out, const int* __restrict__ positions,
+pooled_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pages, const T* __restrict__ pooled_pages, T* __restrict__ out,
+                              const int* __restrict__ positions,
                               const int* __restrict__ token_segment, const int* __restrict__ block_table, const int* __restrict__ pool_table,
                               PooledLayout L, int heads, float scale, float cap, const float* __restrict__ head_bias, int window, int pool,
                               const float* __restrict__ v_freq, int v_interleaved, int* status) {
@@ -192,7 +186,7 @@ pooled_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_p
     float acc[kPooledMaxDims];
 #pragma unroll
     for (int slot = 0; slot < kPooledMaxDims; ++slot) acc[slot] = 0.0f;
-    const int k_width = L.groups * L.dk, v_width = L.groups * L.dv;
+    const int width = L.groups * (L.dk + L.dv);
     const int items = blocks + (position + 1 - first);
     for (int chunk = 0; chunk < items; chunk += kPooledChunk) {
         const int count = min(kPooledChunk, items - chunk);
@@ -208,7 +202,7 @@ pooled_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_p
             } else {
                 const int per_page = pooled ? L.pool_rows : L.page_size;
                 row_index = page * per_page + where % per_page;
-                const T* k_row = (pooled ? pk_pages : k_pages) + static_cast<size_t>(row_index) * k_width + group * L.dk;
+                const T* k_row = (pooled ? pooled_pages : pages) + static_cast<size_t>(row_index) * width + group * (L.dk + L.dv);
                 float dot = 0.0f;
                 for (int d = 0; d < L.dk; ++d) dot += q_s[d] * to_float(k_row[d]);
                 w = pooled_weight(dot, scale, cap, bias);
@@ -225,11 +219,8 @@ pooled_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_p
                 for (int i = 0; i < count; ++i) {
                     const int row_index = rows[i];
                     if (row_index < 0) continue;
-                    const bool pooled = chunk + i < blocks;
-                    const int per_page = pooled ? L.pool_rows : L.page_size;
-                    const int page = row_index / per_page, r = row_index - page * per_page;
-                    const T* base = pooled ? pv_pages : v_pages;
-                    sum += weights[i] * to_float(base[(static_cast<size_t>(page) * v_width + group * L.dv + d) * per_page + r]);
+                    const T* base = chunk + i < blocks ? pooled_pages : pages;
+                    sum += weights[i] * to_float(base[static_cast<size_t>(row_index) * width + group * (L.dk + L.dv) + L.dk + d]);
                 }
                 acc[slot] = sum;
             }
@@ -266,11 +257,231 @@ pooled_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_p
     }
 }
 
+// ------------------------------------------------------------------------------------ tensor cores (bfloat16)
+// A CTA of four warps takes a tile of up to 16 * TB consecutive tokens of one portion and HB query heads of one K/V head
+// (HB * TB = 4: a warp is one head's 16 tokens).  Rows of the cache come 64 at a time through two cp.async stages, first the
+// pooled blocks from block 0 on, then the positions from the multiple of 64 at or below the tile's first visible one: so the
+// tiles a query's keys fall into, and with them the order of its sums, depend on its position alone.  Rows that no query
+// of the CTA sees are zero-filled and never read.  S = Q K^T (m16n8k16, K straight from the rows), the weights in 32-bit with
+// a mask per element, P rounded to bfloat16 as the next product's A operand, O += P V with V through ldmatrix.trans from the
+// same rows.  At the end a head's sums are turned back by the query's position in registers (both channels of a pair lie in
+// one thread) and rounded once.
+constexpr int kPooledMmaKeys = 64, kPooledMmaWarps = 4;
+
+__device__ __forceinline__ void pooled_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void pooled_ldmatrix_x4_trans(uint32_t (&r)[4], const void* shared_address) {
+    const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(shared_address));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+
+// 16 bytes from global to shared memory, or 16 zero bytes (nothing is read) if `valid` is false.
+__device__ __forceinline__ void pooled_copy_16(void* shared_destination, const void* global_source, bool valid) {
+    const uint32_t destination = static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination));
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(destination), "l"(global_source), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ float pooled_tanh(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t pooled_pack(float low, float high) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+// tiles: (first row, count) per tile.  grid (tiles, groups * ceil(heads per group / HB)).  DK, DV: the largest key and
+// value sizes of the instantiation (multiples of 16); the real ones, multiples of 16 too, come in L.
+template <int DK, int DV>
+__global__ void __launch_bounds__(32 * kPooledMmaWarps)
+pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages, const __nv_bfloat16* __restrict__ pooled_pages,
+                            __nv_bfloat16* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ positions,
+                            const int* __restrict__ token_segment, const int* __restrict__ block_table, const int* __restrict__ pool_table,
+                            PooledLayout L, int heads, int head_block, float scale, float cap, const float* __restrict__ head_bias, int window, int pool,
+                            const float* __restrict__ v_freq, int v_interleaved, int* status) {
+    extern __shared__ __align__(16) __nv_bfloat16 pooled_rows[];   // two stages of 64 rows of `pitch` elements
+    const int row_width = L.dk + L.dv, pitch = row_width + 8;      // rows 16 bytes apart modulo 128: no bank is met twice
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int first_row = tiles[2 * blockIdx.x], count = tiles[2 * blockIdx.x + 1];
+    const int per_group = heads / L.groups, head_blocks = (per_group + head_block - 1) / head_block;
+    const int group = blockIdx.y / head_blocks, head_in_group = (blockIdx.y % head_blocks) * head_block + warp % head_block;
+    const int token_block = warp / head_block;                     // the warp's 16 tokens of the tile
+    const bool idle = head_in_group >= per_group || token_block * 16 >= count || token_block >= kPooledMmaWarps / head_block;
+    const int head = group * per_group + (idle ? 0 : head_in_group);
+    const int segment = token_segment[first_row];
+    const int p_first = positions[first_row], p_last = p_first + count - 1;   // a tile's tokens follow one another in a portion
+    const int blocks_seen = pool > 0 ? max(0, p_last - window + 1) / pool : 0;   // by the tile's last token
+    const int first_key = max(0, p_first - window + 1);
+    const int pooled_tiles = (blocks_seen + kPooledMmaKeys - 1) / kPooledMmaKeys;
+    const int first_token_tile = first_key / kPooledMmaKeys, token_tiles = p_last / kPooledMmaKeys - first_token_tile + 1;
+    const int num_tiles = pooled_tiles + token_tiles;
+    const int chunks = row_width / 8;   // 16-byte pieces of a row
+    const size_t group_offset = static_cast<size_t>(group) * row_width, row_stride = static_cast<size_t>(L.groups) * row_width;
+
+    auto load = [&](int stage, int tile) {
+        __nv_bfloat16* destination = pooled_rows + static_cast<size_t>(stage) * kPooledMmaKeys * pitch;
+        const bool pooled = tile < pooled_tiles;
+        const int base = pooled ? tile * kPooledMmaKeys : (first_token_tile + tile - pooled_tiles) * kPooledMmaKeys;
+        for (int index = threadIdx.x; index < kPooledMmaKeys * chunks; index += blockDim.x) {
+            const int row = index / chunks, chunk = index - row * chunks;
+            const int where = base + row;
+            bool valid = pooled ? where < blocks_seen : (where >= first_key && where <= p_last);
+            const __nv_bfloat16* source = pages;
+            if (valid) {
+                const int page = pooled ? pooled_page(pool_table, L, segment, where) : token_page(block_table, L, segment, where);
+                if (page < 0) {
+                    report_error(status, kBadPage);
+                    valid = false;
+                } else {
+                    const int per_page = pooled ? L.pool_rows : L.page_size;
+                    source = (pooled ? pooled_pages : pages) + (static_cast<size_t>(page) * per_page + where % per_page) * row_stride + group_offset + 8 * chunk;
+                }
+            }
+            pooled_copy_16(destination + static_cast<size_t>(row) * pitch + 8 * chunk, source, valid);
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    load(0, 0);
+
+    // the warp's queries as A fragments, its rows' positions and what each of them sees
+    const int row_g = token_block * 16 + g, row_g8 = row_g + 8;
+    const bool live_g = !idle && row_g < count, live_g8 = !idle && row_g8 < count;
+    const int p_g = p_first + row_g, p_g8 = p_first + row_g8;
+    const int seen_g = pool > 0 ? max(0, p_g - window + 1) / pool : 0, seen_g8 = pool > 0 ? max(0, p_g8 - window + 1) / pool : 0;
+    uint32_t q_a[DK / 16][4];
+    {
+        const __nv_bfloat16* q_g = q + (static_cast<size_t>(first_row + row_g) * heads + head) * L.dk;
+        const __nv_bfloat16* q_g8 = q + (static_cast<size_t>(first_row + row_g8) * heads + head) * L.dk;
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+            const bool in_k = 16 * ks < L.dk;
+            q_a[ks][0] = live_g && in_k ? *reinterpret_cast<const uint32_t*>(q_g + 16 * ks + 2 * t) : 0u;
+            q_a[ks][1] = live_g8 && in_k ? *reinterpret_cast<const uint32_t*>(q_g8 + 16 * ks + 2 * t) : 0u;
+            q_a[ks][2] = live_g && in_k ? *reinterpret_cast<const uint32_t*>(q_g + 16 * ks + 8 + 2 * t) : 0u;
+            q_a[ks][3] = live_g8 && in_k ? *reinterpret_cast<const uint32_t*>(q_g8 + 16 * ks + 8 + 2 * t) : 0u;
+        }
+    }
+    const float bias = head_bias != nullptr ? head_bias[head] : 0.0f;
+    const float inverse_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
+    float o[DV / 8][4];
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+
+    for (int tile = 0; tile < num_tiles; ++tile) {
+        const int stage = tile & 1;
+        if (tile + 1 < num_tiles) {
+            load(stage ^ 1, tile + 1);   // that stage was used up in the turn before (the barrier at its end)
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();
+        const bool pooled = tile < pooled_tiles;
+        const int base = pooled ? tile * kPooledMmaKeys : (first_token_tile + tile - pooled_tiles) * kPooledMmaKeys;
+        // a warp none of whose rows sees any of the tile's rows skips the arithmetic
+        const int p_low = p_first + token_block * 16, p_high = min(p_last, p_low + 15);
+        const bool any = !idle && (pooled ? base < (pool > 0 ? max(0, p_high - window + 1) / pool : 0) : (base <= p_high && base + kPooledMmaKeys - 1 + window > p_low));
+        if (any) {
+            const __nv_bfloat16* rows = pooled_rows + static_cast<size_t>(stage) * kPooledMmaKeys * pitch;
+            float sc[kPooledMmaKeys / 8][4];
+#pragma unroll
+            for (int n = 0; n < kPooledMmaKeys / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < DK / 16; ++ks) {
+                if (16 * ks < L.dk) {
+#pragma unroll
+                    for (int n = 0; n < kPooledMmaKeys / 8; ++n) {
+                        const __nv_bfloat16* k_row = rows + static_cast<size_t>(8 * n + g) * pitch + 16 * ks + 2 * t;
+                        pooled_mma(sc[n], q_a[ks], *reinterpret_cast<const uint32_t*>(k_row), *reinterpret_cast<const uint32_t*>(k_row + 8));
+                    }
+                }
+            }
+#pragma unroll
+            for (int n = 0; n < kPooledMmaKeys / 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int where = base + 8 * n + 2 * t + (e & 1);
+                    const bool upper = e < 2;   // row g; else row g + 8
+                    const bool seen = pooled ? where < (upper ? seen_g : seen_g8)
+                                             : (upper ? (live_g && where <= p_g && where + window > p_g) : (live_g8 && where <= p_g8 && where + window > p_g8));
+                    float score = sc[n][e] * scale;
+                    if (cap > 0.0f) score = cap * pooled_tanh(score * inverse_cap);
+                    sc[n][e] = seen ? __fdividef(1.0f, 1.0f + __expf(-(score + bias))) : 0.0f;
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < kPooledMmaKeys / 16; ++kk) {
+                uint32_t p_a[4];
+                p_a[0] = pooled_pack(sc[2 * kk][0], sc[2 * kk][1]);
+                p_a[1] = pooled_pack(sc[2 * kk][2], sc[2 * kk][3]);
+                p_a[2] = pooled_pack(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+                p_a[3] = pooled_pack(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+                // four 8 x 8 pieces of V at a time: keys 16 kk (+8) x channels 16 n (+8); lane l gives the address of row l % 8 of piece l / 8
+                const __nv_bfloat16* v_rows = rows + static_cast<size_t>(16 * kk + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + L.dk + (lane >> 4) * 8;
+#pragma unroll
+                for (int n = 0; n < DV / 16; ++n) {
+                    if (16 * n < L.dv) {
+                        uint32_t v_b[4];
+                        pooled_ldmatrix_x4_trans(v_b, v_rows + 16 * n);
+                        pooled_mma(o[2 * n], p_a, v_b[0], v_b[1]);
+                        pooled_mma(o[2 * n + 1], p_a, v_b[2], v_b[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();   // the stage is refilled in the next turn
+    }
+    if (idle) return;
+    // turned back by the row's position, rounded once; o[n][0..1]: row g, channels 8 n + 2 t (+1); o[n][2..3]: row g + 8
+    const int half_tiles = L.dv / 16;   // channel c and c + dv / 2 lie half_tiles tiles apart, in the same thread
+#pragma unroll
+    for (int upper = 0; upper < 2; ++upper) {
+        if (!(upper == 0 ? live_g : live_g8)) continue;
+        const float p = static_cast<float>(upper == 0 ? p_g : p_g8);
+        __nv_bfloat16* destination = out + (static_cast<size_t>(first_row + (upper == 0 ? row_g : row_g8)) * heads + head) * L.dv;
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n) {
+            if (8 * n >= L.dv) continue;
+            float low = o[n][2 * upper], high = o[n][2 * upper + 1];
+            if (v_freq != nullptr) {
+                float sine, cosine;
+                if (v_interleaved) {
+                    sincosf(p * v_freq[4 * n + t], &sine, &cosine);
+                    const float a = low, b = high;
+                    low = a * cosine + b * sine;
+                    high = b * cosine - a * sine;
+                } else {
+                    const bool first_half = n < half_tiles;
+                    const int partner = first_half ? n + half_tiles : n - half_tiles;
+                    const int pair = 8 * (first_half ? n : partner) + 2 * t;
+                    float other_low = 0.0f, other_high = 0.0f;
+#pragma unroll
+                    for (int m = 0; m < DV / 8; ++m)
+                        if (m == partner) other_low = o[m][2 * upper], other_high = o[m][2 * upper + 1];
+                    sincosf(p * v_freq[pair], &sine, &cosine);
+                    const float turned_low = first_half ? low * cosine + other_low * sine : low * cosine - other_low * sine;
+                    sincosf(p * v_freq[pair + 1], &sine, &cosine);
+                    const float turned_high = first_half ? high * cosine + other_high * sine : high * cosine - other_high * sine;
+                    low = turned_low, high = turned_high;
+                }
+            }
+            *reinterpret_cast<uint32_t*>(destination + 8 * n + 2 * t) = pooled_pack(low, high);
+        }
+    }
+}
+
 }  // namespace lb
 
 extern "C" {
 
-int lb_pooled_rewrite(const void* qkv, int stride, void* q_out, void* k_pages, void* v_pages, const float* qk_freq, int rot_dims, int qk_interleaved,
+int lb_pooled_rewrite(const void* qkv, int stride, void* q_out, void* pages, const float* qk_freq, int rot_dims, int qk_interleaved,
                       const float* v_freq, int v_interleaved, const int* positions, const int* token_segment, const int* block_table, int tokens,
                       int heads, int groups, int dk, int dv, int page_size, int num_pages, int max_blocks, int write_kv, int dtype, int* status,
                       cudaStream_t stream) {
@@ -278,15 +489,14 @@ int lb_pooled_rewrite(const void* qkv, int stride, void* q_out, void* k_pages, v
     if (heads % groups != 0 || rot_dims < 0 || rot_dims > dk || rot_dims % 2 != 0 || (v_freq != nullptr && dv % 2 != 0)) return -2;
     lb::PooledLayout L{page_size, num_pages, max_blocks, 1, 0, 0, groups, dk, dv};
     LB_DISPATCH_DTYPE(dtype, {
-        lb::pooled_rewrite_kernel<T><<<tokens, 256, 0, stream>>>(static_cast<const T*>(qkv), stride, static_cast<T*>(q_out), static_cast<T*>(k_pages),
-                                                                  static_cast<T*>(v_pages), qk_freq, rot_dims, qk_interleaved, v_freq, v_interleaved, positions,
+        lb::pooled_rewrite_kernel<T><<<tokens, 256, 0, stream>>>(static_cast<const T*>(qkv), stride, static_cast<T*>(q_out), static_cast<T*>(pages), qk_freq, rot_dims, qk_interleaved, v_freq, v_interleaved, positions,
                                                                   token_segment, block_table, L, heads, write_kv, status);
     })
     return LB_LAUNCH_RESULT();
 }
 
 // max_length: the longest portion of the step (a portion of n tokens completes at most n / pool + 1 blocks).
-int lb_pooled_means(const void* k_pages, const void* v_pages, void* pk_pages, void* pv_pages, const int* segment_length, const int* segment_context,
+int lb_pooled_means(const void* pages, void* pooled_pages, const int* segment_length, const int* segment_context,
                     const int* block_table, const int* pool_table, int segments, int max_length, int groups, int dk, int dv, int page_size, int num_pages,
                     int max_blocks, int pool_rows, int pool_pages, int pool_max_blocks, int pool, int dtype, int* status, cudaStream_t stream) {
     if (segments == 0 || max_length == 0) return 0;
@@ -294,13 +504,12 @@ int lb_pooled_means(const void* k_pages, const void* v_pages, void* pk_pages, vo
     lb::PooledLayout L{page_size, num_pages, max_blocks, pool_rows, pool_pages, pool_max_blocks, groups, dk, dv};
     const dim3 grid(segments, max_length / pool + 1);
     LB_DISPATCH_DTYPE(dtype, {
-        lb::pooled_means_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(k_pages), static_cast<const T*>(v_pages), static_cast<T*>(pk_pages),
-                                                              static_cast<T*>(pv_pages), segment_length, segment_context, block_table, pool_table, L, pool, status);
+        lb::pooled_means_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(pages), static_cast<T*>(pooled_pages), segment_length, segment_context, block_table, pool_table, L, pool, status);
     })
     return LB_LAUNCH_RESULT();
 }
 
-int lb_pooled_attention_plain(const void* q, const void* k_pages, const void* v_pages, const void* pk_pages, const void* pv_pages, void* out,
+int lb_pooled_attention_plain(const void* q, const void* pages, const void* pooled_pages, void* out,
                               const int* positions, const int* token_segment, const int* block_table, const int* pool_table, int tokens, int heads,
                               int groups, int dk, int dv, int page_size, int num_pages, int max_blocks, int pool_rows, int pool_pages, int pool_max_blocks,
                               float scale, float cap, const float* head_bias, int window, int pool, const float* v_freq, int v_interleaved, int dtype,
@@ -312,10 +521,40 @@ int lb_pooled_attention_plain(const void* q, const void* k_pages, const void* v_
     if (shared > 48 * 1024) return -2;
     LB_DISPATCH_DTYPE(dtype, {
         lb::pooled_attention_plain_kernel<T><<<dim3(tokens, heads), lb::kPooledThreads, shared, stream>>>(
-            static_cast<const T*>(q), static_cast<const T*>(k_pages), static_cast<const T*>(v_pages), static_cast<const T*>(pk_pages),
-            static_cast<const T*>(pv_pages), static_cast<T*>(out), positions, token_segment, block_table, pool_table, L, heads, scale, cap, head_bias, window,
+            static_cast<const T*>(q), static_cast<const T*>(pages), static_cast<const T*>(pooled_pages), static_cast<T*>(out), positions, token_segment, block_table, pool_table, L, heads, scale, cap, head_bias, window,
             pool, v_freq, v_interleaved, status);
     })
+    return LB_LAUNCH_RESULT();
+}
+
+// head_block: the query heads of a K/V head that one CTA takes (1 to 4; its tiles have 64 / head_block tokens at most... 16 * (4 / head_block)).
+int lb_pooled_attention_mma(const void* q, const void* pages, const void* pooled_pages, void* out, const int* tiles, int num_tiles, const int* positions,
+                            const int* token_segment, const int* block_table, const int* pool_table, int heads, int groups, int dk, int dv, int page_size,
+                            int num_pages, int max_blocks, int pool_rows, int pool_pages, int pool_max_blocks, int head_block, float scale, float cap,
+                            const float* head_bias, int window, int pool, const float* v_freq, int v_interleaved, int* status, cudaStream_t stream) {
+    if (num_tiles == 0) return 0;
+    if (heads % groups != 0 || dk % 16 != 0 || dv % 16 != 0 || dk < 16 || dv < 16 || dk > 128 || dv > 128 || window < 1 || pool < 0 || head_block < 1 || head_block > 4) return -2;
+    lb::PooledLayout L{page_size, num_pages, max_blocks, pool_rows > 0 ? pool_rows : 1, pool_pages, pool_max_blocks, groups, dk, dv};
+    const int per_group = heads / groups;
+    const dim3 grid(num_tiles, groups * ((per_group + head_block - 1) / head_block));
+    const size_t shared = 2 * static_cast<size_t>(lb::kPooledMmaKeys) * (dk + dv + 8) * sizeof(__nv_bfloat16);
+    const auto* q16 = static_cast<const __nv_bfloat16*>(q);
+    const auto* pages16 = static_cast<const __nv_bfloat16*>(pages);
+    const auto* pooled16 = static_cast<const __nv_bfloat16*>(pooled_pages);
+    auto* out16 = static_cast<__nv_bfloat16*>(out);
+    if (dk <= 64 && dv <= 64) {
+        static lb::OncePerDevice once;
+        lb::allow_shared_memory(once, lb::pooled_attention_mma_kernel<64, 64>, 2 * lb::kPooledMmaKeys * (128 + 8) * 2);
+        lb::pooled_attention_mma_kernel<64, 64><<<grid, 32 * lb::kPooledMmaWarps, shared, stream>>>(
+            q16, pages16, pooled16, out16, tiles, positions, token_segment, block_table, pool_table, L, heads, head_block, scale, cap, head_bias, window, pool, v_freq,
+            v_interleaved, status);
+    } else {
+        static lb::OncePerDevice once;
+        lb::allow_shared_memory(once, lb::pooled_attention_mma_kernel<128, 128>, 2 * lb::kPooledMmaKeys * (256 + 8) * 2);
+        lb::pooled_attention_mma_kernel<128, 128><<<grid, 32 * lb::kPooledMmaWarps, shared, stream>>>(
+            q16, pages16, pooled16, out16, tiles, positions, token_segment, block_table, pool_table, L, heads, head_block, scale, cap, head_bias, window, pool, v_freq,
+            v_interleaved, status);
+    }
     return LB_LAUNCH_RESULT();
 }
 

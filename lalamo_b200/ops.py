@@ -1396,28 +1396,28 @@ def linear_attention(proj: torch.Tensor, matrix_state: torch.Tensor, *, num_head
 
 
 # ------------------------------------------------------------- pooled window attention
-def _check_pooled(k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor, groups: int, head_dim: int, value_dim: int, what: str) -> tuple[int, int, int]:
-    _check(k_pages, f"{what} key pages")
-    _check(v_pages, f"{what} value pages", k_pages.dtype)
+def _check_pooled(pages: torch.Tensor, block_table: torch.Tensor, groups: int, head_dim: int, value_dim: int, what: str) -> tuple[int, int, int]:
+    _check(pages, f"{what} pages")
     _check(block_table, f"{what} block table", torch.int32)
-    pages, rows = k_pages.shape[0], k_pages.shape[1]
-    if k_pages.shape != (pages, rows, groups, head_dim) or v_pages.shape != (pages, groups, value_dim, rows) or block_table.dim() != 2:
-        raise KernelError(f"pooled attention: the {what} pages must be [pages, rows, groups, head_dim] and [pages, groups, value_dim, rows]")
-    return pages, rows, block_table.shape[1]
+    count, rows = pages.shape[0], pages.shape[1]
+    if pages.shape != (count, rows, groups, head_dim + value_dim) or block_table.dim() != 2:
+        raise KernelError(f"pooled attention: the {what} pages must be [pages, rows, groups, head_dim + value_dim] (a row holds key and value)")
+    return count, rows, block_table.shape[1]
 
 
-def pooled_rewrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, *, qk_freq: torch.Tensor | None, rotary_dim: int,
+def pooled_rewrite(qkv: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor, *, qk_freq: torch.Tensor | None, rotary_dim: int,
                    value_freq: torch.Tensor | None, interleaved: bool = False, positions: torch.Tensor, token_segment: torch.Tensor, block_table: torch.Tensor,
                    num_heads: int, num_groups: int, head_dim: int, value_dim: int, write_kv: bool, status: torch.Tensor) -> None:
     """Splits the rows of ``qkv`` (q ``heads x head_dim`` | k ``groups x head_dim`` | v ``groups x value_dim``; a column slice of a wider
     product will do) into heads, rotates the first ``rotary_dim`` channels of q and k by the token's position (``qk_freq``: a 32-bit
     frequency per pair) and, with ``value_freq`` (``value_dim / 2`` frequencies), all channels of v; q goes to ``q_out``, k and v
-    into the token's page row.  Angles, sines and cosines in 32-bit, one rounding."""
+    into the token's page row (``pages`` ``[pages, page_size, groups, head_dim + value_dim]``).  Angles, sines and cosines in 32-bit,
+    one rounding."""
     if not qkv.is_cuda or qkv.dim() != 2 or qkv.stride(1) != 1:
         raise KernelError("pooled_rewrite: qkv must be a [tokens, .] CUDA tensor with unit column stride")
     _check(q_out, "q_out", qkv.dtype)
-    pages, page_size, max_blocks = _check_pooled(k_pages, v_pages, block_table, num_groups, head_dim, value_dim, "token")
-    if k_pages.dtype != qkv.dtype:
+    count, page_size, max_blocks = _check_pooled(pages, block_table, num_groups, head_dim, value_dim, "token")
+    if pages.dtype != qkv.dtype:
         raise KernelError("pooled_rewrite: the pages must have qkv's type")
     tokens = qkv.shape[0]
     if qkv.shape[1] < num_heads * head_dim + num_groups * (head_dim + value_dim) or q_out.shape != (tokens, num_heads * head_dim):
@@ -1432,67 +1432,112 @@ def pooled_rewrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor
             raise KernelError("pooled_rewrite: rotated values need an even value_dim and one frequency per pair")
     for name, tensor in (("positions", positions), ("token_segment", token_segment)):
         _check(tensor, name, torch.int32)
-    code = _lib().lb_pooled_rewrite(_ptr(qkv), c_int(qkv.stride(0)), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(qk_freq if rotary_dim else None), c_int(rotary_dim),
+    code = _lib().lb_pooled_rewrite(_ptr(qkv), c_int(qkv.stride(0)), _ptr(q_out), _ptr(pages), _ptr(qk_freq if rotary_dim else None), c_int(rotary_dim),
                                     c_int(1 if interleaved else 0), _ptr(value_freq), c_int(1 if interleaved else 0), _ptr(positions), _ptr(token_segment),
                                     _ptr(block_table), c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(value_dim), c_int(page_size),
-                                    c_int(pages), c_int(max_blocks), c_int(1 if write_kv else 0), c_int(dtype_code(qkv.dtype)), _ptr(status), _stream())
+                                    c_int(count), c_int(max_blocks), c_int(1 if write_kv else 0), c_int(dtype_code(qkv.dtype)), _ptr(status), _stream())
     _done(code, "pooled_rewrite")
 
 
-def pooled_means(k_pages: torch.Tensor, v_pages: torch.Tensor, pool_k_pages: torch.Tensor, pool_v_pages: torch.Tensor, *, segment_length: torch.Tensor,
-                 segment_context: torch.Tensor, block_table: torch.Tensor, pool_table: torch.Tensor, segments: int, max_length: int, num_groups: int,
-                 head_dim: int, value_dim: int, pool: int, status: torch.Tensor) -> None:
+def pooled_means(pages: torch.Tensor, pool_pages: torch.Tensor, *, segment_length: torch.Tensor, segment_context: torch.Tensor, block_table: torch.Tensor,
+                 pool_table: torch.Tensor, segments: int, max_length: int, num_groups: int, head_dim: int, value_dim: int, pool: int, status: torch.Tensor) -> None:
     """For every block of ``pool`` positions whose last position this step wrote: the mean of its keys and of its values as the
     token pages hold them (32-bit sums in the order of the positions, one rounding) into row ``b % rows`` of the request's pooled
     page ``pool_table[b / rows]``.  ``max_length``: the step's longest portion."""
-    pages, page_size, max_blocks = _check_pooled(k_pages, v_pages, block_table, num_groups, head_dim, value_dim, "token")
-    pool_pages, pool_rows, pool_blocks = _check_pooled(pool_k_pages, pool_v_pages, pool_table, num_groups, head_dim, value_dim, "pooled")
-    if pool_k_pages.dtype != k_pages.dtype or pool < 1:
+    count, page_size, max_blocks = _check_pooled(pages, block_table, num_groups, head_dim, value_dim, "token")
+    pool_count, pool_rows, pool_blocks = _check_pooled(pool_pages, pool_table, num_groups, head_dim, value_dim, "pooled")
+    if pool_pages.dtype != pages.dtype or pool < 1:
         raise KernelError("pooled_means: pages of one type and a positive block size")
     for name, tensor in (("segment_length", segment_length), ("segment_context", segment_context)):
         _check(tensor, name, torch.int32)
-    code = _lib().lb_pooled_means(_ptr(k_pages), _ptr(v_pages), _ptr(pool_k_pages), _ptr(pool_v_pages), _ptr(segment_length), _ptr(segment_context), _ptr(block_table),
+    code = _lib().lb_pooled_means(_ptr(pages), _ptr(pool_pages), _ptr(segment_length), _ptr(segment_context), _ptr(block_table),
                                   _ptr(pool_table), c_int(segments), c_int(max_length), c_int(num_groups), c_int(head_dim), c_int(value_dim), c_int(page_size),
-                                  c_int(pages), c_int(max_blocks), c_int(pool_rows), c_int(pool_pages), c_int(pool_blocks), c_int(pool), c_int(dtype_code(k_pages.dtype)),
+                                  c_int(count), c_int(max_blocks), c_int(pool_rows), c_int(pool_count), c_int(pool_blocks), c_int(pool), c_int(dtype_code(pages.dtype)),
                                   _ptr(status), _stream())
     _done(code, "pooled_means")
 
 
-def pooled_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pool_k_pages: torch.Tensor | None, pool_v_pages: torch.Tensor | None,
-                           out: torch.Tensor, *, positions: torch.Tensor, token_segment: torch.Tensor, block_table: torch.Tensor, pool_table: torch.Tensor | None,
-                           num_heads: int, num_groups: int, head_dim: int, value_dim: int, scale: float, softcap: float, head_bias: torch.Tensor | None,
-                           window: int, pool: int, value_freq: torch.Tensor | None, interleaved: bool = False, status: torch.Tensor) -> None:
-    """Sigmoid-weighted attention of every token over the positions of its window and the pooled blocks wholly before it:
-    ``out[t, h] = sum_x sigmoid(cap(q . k_x * scale) + head_bias[h]) v_x`` (no normalisation), blocks first, then positions
-    upwards, all in 32-bit; with ``value_freq`` the sum is turned back by the token's position.  One block per token and head."""
+POOLED_MMA_HEADS = 4  # query heads of one K/V head that a CTA of the tensor-core kernel takes at most
+
+
+def pooled_attention_tiling(num_heads: int, num_groups: int) -> tuple[int, int]:
+    """``(query heads of a K/V head per CTA, tokens per tile)`` of the tensor-core kernel: a CTA's four warps are one head's 16 tokens each."""
+    head_block = min(num_heads // num_groups, POOLED_MMA_HEADS)
+    return head_block, 16 * (4 // head_block)
+
+
+def pooled_attention_supported(dtype: torch.dtype, head_dim: int, value_dim: int) -> bool:
+    """Whether the tensor-core kernel takes these sizes (bfloat16, heads of multiples of 16 up to 128 channels)."""
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= head_dim <= 128 and 16 <= value_dim <= 128
+
+
+def _pooled_arguments(q, pages, pool_pages, out, positions, token_segment, block_table, pool_table, num_heads, num_groups, head_dim, value_dim, head_bias,
+                      window, pool, value_freq, what):
     _check(q, "q")
     _check(out, "out", q.dtype)
-    pages, page_size, max_blocks = _check_pooled(k_pages, v_pages, block_table, num_groups, head_dim, value_dim, "token")
+    count, page_size, max_blocks = _check_pooled(pages, block_table, num_groups, head_dim, value_dim, "token")
     if pool:
-        pool_pages, pool_rows, pool_blocks = _check_pooled(pool_k_pages, pool_v_pages, pool_table, num_groups, head_dim, value_dim, "pooled")
+        pool_count, pool_rows, pool_blocks = _check_pooled(pool_pages, pool_table, num_groups, head_dim, value_dim, "pooled")
     else:
-        pool_pages, pool_rows, pool_blocks = 0, 1, 0
+        pool_count, pool_rows, pool_blocks = 0, 1, 0
     tokens = q.shape[0]
-    if q.shape != (tokens, num_heads * head_dim) or out.shape != (tokens, num_heads * value_dim) or k_pages.dtype != q.dtype or num_heads % num_groups:
-        raise KernelError("pooled_attention_plain: q, out or the pages do not fit the head counts")
+    if q.shape != (tokens, num_heads * head_dim) or out.shape != (tokens, num_heads * value_dim) or pages.dtype != q.dtype or num_heads % num_groups:
+        raise KernelError(f"{what}: q, out or the pages do not fit the head counts")
     if head_bias is not None:
         _check(head_bias, "head_bias", torch.float32)
         if head_bias.numel() != num_heads:
-            raise KernelError("pooled_attention_plain: one bias per head")
+            raise KernelError(f"{what}: one bias per head")
     if value_freq is not None:
         _check(value_freq, "value_freq", torch.float32)
         if value_dim % 2 or value_freq.numel() != value_dim // 2:
-            raise KernelError("pooled_attention_plain: rotated values need an even value_dim and one frequency per pair")
+            raise KernelError(f"{what}: rotated values need an even value_dim and one frequency per pair")
     if window < 1 or pool < 0 or value_dim > 512:
-        raise KernelError("pooled_attention_plain: a positive window, a block size that is not negative and values of at most 512 channels")
+        raise KernelError(f"{what}: a positive window, a block size that is not negative and values of at most 512 channels")
     for name, tensor in (("positions", positions), ("token_segment", token_segment)):
         _check(tensor, name, torch.int32)
-    code = _lib().lb_pooled_attention_plain(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(pool_k_pages if pool else None), _ptr(pool_v_pages if pool else None), _ptr(out),
+    return tokens, (count, page_size, max_blocks), (pool_count, pool_rows, pool_blocks)
+
+
+def pooled_attention_plain(q: torch.Tensor, pages: torch.Tensor, pool_pages: torch.Tensor | None, out: torch.Tensor, *, positions: torch.Tensor,
+                           token_segment: torch.Tensor, block_table: torch.Tensor, pool_table: torch.Tensor | None, num_heads: int, num_groups: int,
+                           head_dim: int, value_dim: int, scale: float, softcap: float, head_bias: torch.Tensor | None, window: int, pool: int,
+                           value_freq: torch.Tensor | None, interleaved: bool = False, status: torch.Tensor) -> None:
+    """Sigmoid-weighted attention of every token over the positions of its window and the pooled blocks wholly before it:
+    ``out[t, h] = sum_x sigmoid(cap(q . k_x * scale) + head_bias[h]) v_x`` (no normalisation), blocks first, then positions
+    upwards, all in 32-bit; with ``value_freq`` the sum is turned back by the token's position.  One block per token and head."""
+    tokens, (count, page_size, max_blocks), (pool_count, pool_rows, pool_blocks) = _pooled_arguments(
+        q, pages, pool_pages, out, positions, token_segment, block_table, pool_table, num_heads, num_groups, head_dim, value_dim, head_bias, window, pool,
+        value_freq, "pooled_attention_plain")
+    code = _lib().lb_pooled_attention_plain(_ptr(q), _ptr(pages), _ptr(pool_pages if pool else None), _ptr(out),
                                             _ptr(positions), _ptr(token_segment), _ptr(block_table), _ptr(pool_table if pool else None), c_int(tokens), c_int(num_heads),
-                                            c_int(num_groups), c_int(head_dim), c_int(value_dim), c_int(page_size), c_int(pages), c_int(max_blocks), c_int(pool_rows),
-                                            c_int(pool_pages), c_int(pool_blocks), c_float(scale), c_float(softcap), _ptr(head_bias), c_int(window), c_int(pool),
+                                            c_int(num_groups), c_int(head_dim), c_int(value_dim), c_int(page_size), c_int(count), c_int(max_blocks), c_int(pool_rows),
+                                            c_int(pool_count), c_int(pool_blocks), c_float(scale), c_float(softcap), _ptr(head_bias), c_int(window), c_int(pool),
                                             _ptr(value_freq), c_int(1 if interleaved else 0), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
     _done(code, "pooled_attention_plain")
+
+
+def pooled_attention(q: torch.Tensor, pages: torch.Tensor, pool_pages: torch.Tensor | None, out: torch.Tensor, *, tiles: torch.Tensor, num_tiles: int,
+                     positions: torch.Tensor, token_segment: torch.Tensor, block_table: torch.Tensor, pool_table: torch.Tensor | None, num_heads: int,
+                     num_groups: int, head_dim: int, value_dim: int, scale: float, softcap: float, head_bias: torch.Tensor | None, window: int, pool: int,
+                     value_freq: torch.Tensor | None, interleaved: bool = False, status: torch.Tensor) -> None:
+    """The same attention on the tensor cores (bfloat16; see :func:`pooled_attention_supported`).  ``tiles``: int32 ``(first row, count)``
+    per tile of consecutive tokens of one portion, at most :func:`pooled_attention_tiling`'s tokens each.  Weights in 32-bit (the cap's
+    tanh and the sigmoid's exponential by the fast units), rounded to bfloat16 for the product with the values; sums in 32-bit."""
+    tokens, (count, page_size, max_blocks), (pool_count, pool_rows, pool_blocks) = _pooled_arguments(
+        q, pages, pool_pages, out, positions, token_segment, block_table, pool_table, num_heads, num_groups, head_dim, value_dim, head_bias, window, pool,
+        value_freq, "pooled_attention")
+    if not pooled_attention_supported(q.dtype, head_dim, value_dim):
+        raise KernelError("pooled_attention: the tensor-core kernel takes bfloat16 and heads of multiples of 16 up to 128 channels")
+    _check(tiles, "tiles", torch.int32)
+    if tiles.numel() < 2 * num_tiles:
+        raise KernelError("pooled_attention: fewer tile records than tiles")
+    head_block, _ = pooled_attention_tiling(num_heads, num_groups)
+    code = _lib().lb_pooled_attention_mma(_ptr(q), _ptr(pages), _ptr(pool_pages if pool else None), _ptr(out), _ptr(tiles), c_int(num_tiles), _ptr(positions),
+                                          _ptr(token_segment), _ptr(block_table), _ptr(pool_table if pool else None), c_int(num_heads), c_int(num_groups),
+                                          c_int(head_dim), c_int(value_dim), c_int(page_size), c_int(count), c_int(max_blocks), c_int(pool_rows), c_int(pool_count),
+                                          c_int(pool_blocks), c_int(head_block), c_float(scale), c_float(softcap), _ptr(head_bias), c_int(window), c_int(pool),
+                                          _ptr(value_freq), c_int(1 if interleaved else 0), _ptr(status), _stream())
+    _done(code, "pooled_attention")
 
 
 # ------------------------------------------------------------------------------ sampling

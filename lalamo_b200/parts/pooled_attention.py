@@ -1,22 +1,24 @@
 """Grouped attention with sigmoid weights under a sliding window, with one mean key and mean value for every whole block
 of positions before the window (see :class:`~lalamo_b200.config.plan.PooledWindowAttentionSpec`).
 
-The mixer holds two paged caches: the positions' keys and values under the window's retention rule (pages go back once
-the window and every unfinished block have passed them), and the blocks' means, one row per block, which are kept for
-good.  A step rotates q, k and v and writes the pages, computes the mean of every block it completed from the pages, and
+The mixer holds two paged caches whose rows hold a key and its value side by side: the positions' under the window's
+retention rule (pages go back once the window and every unfinished block have passed them), and the blocks' means, one
+row per block, which are kept for good.  A step rotates q, k and v and writes the pages, computes the mean of every block it completed from the pages, and
 then attends: the visible blocks first, then the window's positions upwards, the weights ``sigmoid(cap(q . k scale) +
 bias_h)`` summed with the values in 32-bit without any normalisation; rotated values are turned back by the query's
-position at the end."""
+position at the end.  In bfloat16, for heads of multiples of 16 channels, the attention runs on the tensor cores in tiles of
+consecutive tokens (single decoded tokens are tiles of one); otherwise, and in 32-bit, a block per token and head computes it plainly."""
 
 from __future__ import annotations
 
 from typing import Mapping
 
+import numpy as np
 import torch
 
 from .. import ops
 from ..config.plan import PooledWindowAttentionSpec, RopeSpec
-from .base import CacheNeed, CompositeNeed, CompositeView, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, register_part
+from .base import CacheNeed, CompositeNeed, CompositeView, HostSegments, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, register_part
 
 __all__ = ["PooledWindowAttention"]
 
@@ -53,6 +55,8 @@ class PooledWindowAttention(Mixer):
         self.qk_freq = _frequencies(self.rotary_dim, spec.position.theta).to(runtime.device) if self.rotary_dim else None
         self.value_freq = _frequencies(spec.value_dim, spec.position.theta).to(runtime.device) if spec.rotate_values else None
         self.scale = spec.scale if spec.scale is not None else spec.head_dim ** -0.5
+        self.on_tensor_cores = ops.pooled_attention_supported(runtime.dtype, spec.head_dim, spec.value_dim)
+        self.tile_tokens = ops.pooled_attention_tiling(spec.num_heads, spec.num_groups)[1]
 
     @classmethod
     def tensor_decls(cls, spec: PooledWindowAttentionSpec) -> dict[str, TensorDecl]:
@@ -69,11 +73,25 @@ class PooledWindowAttention(Mixer):
     def cache_need(self) -> CacheNeed | None:
         spec = self.spec
         # A block's mean is taken when its last position is written: until then its positions stay, also behind the window.
-        tokens = PagedKVNeed(num_groups=spec.num_groups, head_dim=spec.head_dim, window=max(spec.window, spec.pool), value_dim=spec.value_dim)
+        row = spec.head_dim + spec.value_dim   # a row holds a key and its value
+        tokens = PagedKVNeed(num_groups=spec.num_groups, head_dim=row, window=max(spec.window, spec.pool), values_in_keys=True)
         if not spec.pool:
             return tokens
-        blocks = PagedKVNeed(num_groups=spec.num_groups, head_dim=spec.head_dim, window=None, value_dim=spec.value_dim, tokens_per_row=spec.pool)
+        blocks = PagedKVNeed(num_groups=spec.num_groups, head_dim=row, window=None, values_in_keys=True, tokens_per_row=spec.pool)
         return CompositeNeed((tokens, blocks))
+
+    # The tensor-core kernel's tiles depend on where the portions start and how long they are, not on what the cache holds,
+    # and are the same for every layer of this kind with the same number of tokens a tile.
+    step_plan_uses_context = False
+
+    def step_plan_key(self) -> object:
+        return ("pooled_window_attention", self.tile_tokens)
+
+    def plan_step(self, segments: HostSegments) -> dict[str, np.ndarray]:
+        """``tiles``: ``(first row, count)`` of each run of at most ``tile_tokens`` consecutive tokens of a portion."""
+        tiles = [(first, min(self.tile_tokens, start + length - first)) for start, length in zip(segments.start, segments.length)
+                 for first in range(start, start + length, self.tile_tokens)]
+        return {"tiles": np.asarray(tiles, dtype=np.int32).reshape(-1)}
 
     can_accumulate = True
 
@@ -87,20 +105,24 @@ class PooledWindowAttention(Mixer):
         qkv = ops.linear(x, self.qkv, status=status)
         queries = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
         shape = dict(num_heads=spec.num_heads, num_groups=spec.num_groups, head_dim=spec.head_dim, value_dim=spec.value_dim)
-        ops.pooled_rewrite(qkv, queries, tokens_view.k_pages, tokens_view.v_pages, qk_freq=self.qk_freq, rotary_dim=self.rotary_dim, value_freq=self.value_freq,
+        ops.pooled_rewrite(qkv, queries, tokens_view.k_pages, qk_freq=self.qk_freq, rotary_dim=self.rotary_dim, value_freq=self.value_freq,
                            interleaved=self.interleaved, positions=step.positions, token_segment=step.token_segment, block_table=tokens_view.block_table,
                            write_kv=tokens_view.owns, status=status, **shape)
         if blocks_view is not None and blocks_view.owns:
-            ops.pooled_means(tokens_view.k_pages, tokens_view.v_pages, blocks_view.k_pages, blocks_view.v_pages, segment_length=step.segment_length,
+            ops.pooled_means(tokens_view.k_pages, blocks_view.k_pages, segment_length=step.segment_length,
                              segment_context=step.segment_context, block_table=tokens_view.block_table, pool_table=blocks_view.block_table,
                              segments=step.segments, max_length=step.max_segment_length, num_groups=spec.num_groups, head_dim=spec.head_dim,
                              value_dim=spec.value_dim, pool=spec.pool, status=status)
         mixed = self.runtime.empty(step.tokens, spec.num_heads * spec.value_dim)
-        ops.pooled_attention_plain(queries, tokens_view.k_pages, tokens_view.v_pages, blocks_view.k_pages if blocks_view is not None else None,
-                                   blocks_view.v_pages if blocks_view is not None else None, mixed, positions=step.positions, token_segment=step.token_segment,
-                                   block_table=tokens_view.block_table, pool_table=blocks_view.block_table if blocks_view is not None else None,
-                                   scale=self.scale, softcap=spec.softcap, head_bias=self.head_bias, window=spec.window, pool=spec.pool,
-                                   value_freq=self.value_freq, interleaved=self.interleaved, status=status, **shape)
+        common = dict(positions=step.positions, token_segment=step.token_segment, block_table=tokens_view.block_table,
+                      pool_table=blocks_view.block_table if blocks_view is not None else None, scale=self.scale, softcap=spec.softcap, head_bias=self.head_bias,
+                      window=spec.window, pool=spec.pool, value_freq=self.value_freq, interleaved=self.interleaved, status=status, **shape)
+        pool_pages = blocks_view.k_pages if blocks_view is not None else None
+        if self.on_tensor_cores:
+            lists, host_lists = step.plan_of(self)
+            ops.pooled_attention(queries, tokens_view.k_pages, pool_pages, mixed, tiles=lists["tiles"], num_tiles=host_lists["tiles"].size // 2, **common)
+        else:
+            ops.pooled_attention_plain(queries, tokens_view.k_pages, pool_pages, mixed, **common)
         if residual is not None:
             return ops.linear_accumulate(mixed, self.out_proj, residual, status=status)
         return ops.linear(mixed, self.out_proj, status=status)

@@ -114,14 +114,14 @@ def test_a_checkpoint_that_does_not_fit_is_reported_whole(tmp_path):
 
 def test_caches_and_states_the_layers_ask_for():
     """Retention: one 32-bit matrix state.  The pair of mixers: the attention's pages under the window's rule (no shorter than a block),
-    its blocks' pages kept for good with one row for every ``pool`` positions, and the linear attention's matrix state."""
+    its blocks' pages kept for good with one row for every ``pool`` positions (a row holds a key and its value), and the linear attention's matrix state."""
     from lalamo_b200.cache.manager import CacheManager
     from lalamo_b200.parts.base import CompositeNeed, PagedKVNeed, SlotStateNeed
 
     # what the parts would declare, spelled out here for CONFIG_A's second and third layer and CONFIG_B's first
     def needs(heads, groups, dim, vdim, size, pool, linear):
-        return CompositeNeed((CompositeNeed((PagedKVNeed(groups, dim, window=max(size, pool), value_dim=vdim),
-                                             PagedKVNeed(groups, dim, window=None, value_dim=vdim, tokens_per_row=pool))),
+        return CompositeNeed((CompositeNeed((PagedKVNeed(groups, dim + vdim, window=max(size, pool), values_in_keys=True),
+                                             PagedKVNeed(groups, dim + vdim, window=None, values_in_keys=True, tokens_per_row=pool))),
                               SlotStateNeed(linear, torch.float32)))
 
     all_needs = [SlotStateNeed((4, 16, 24), torch.float32), needs(4, 2, 16, 24, 37, 5, (2, 16, 8)), needs(2, 2, 32, 16, 16, 16, (4, 8, 16)), needs(3, 3, 24, 10, 9, 21, (1, 12, 20))]

@@ -239,10 +239,11 @@ def test_router_with_a_choice_bias_and_experts_without_a_gate():
     assert torch.allclose(stream.double().cpu(), want + scores[:, experts : experts + 1] * shared.double(), rtol=2e-2, atol=2e-2)
 
 
-def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size, contexts, lengths, cap, seed):
+def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size, contexts, lengths, cap, seed, tensor_cores=False):
     """One step of the pooled attention's kernels over requests that hold ``contexts`` tokens already and bring ``lengths`` more (the
     earlier tokens go through the same kernels, one request a step, in uneven portions), against the plain attention over each
-    request's whole sequence.  Pages are handed out in a scattered order."""
+    request's whole sequence.  Pages are handed out in a scattered order.  ``tensor_cores``: the last step's attention on the tensor-core
+    kernel, in tiles of consecutive tokens."""
     from lalamo_b200 import ops
 
     device = torch.device("cuda")
@@ -257,16 +258,14 @@ def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size,
     pool_rows = -(-page_size // pool)
     order = torch.randperm(pages, generator=generator).tolist()
     table = torch.tensor([[order[r * blocks_per_request + b] for b in range(blocks_per_request)] for r in range(len(totals))], dtype=torch.int32, device=device)
-    k_pages = torch.full((pages, page_size, groups, dk), float("nan"), dtype=dtype, device=device)
-    v_pages = torch.full((pages, groups, dv, page_size), float("nan"), dtype=dtype, device=device)
-    pk_pages = torch.full((pages, pool_rows, groups, dk), float("nan"), dtype=dtype, device=device)
-    pv_pages = torch.full((pages, groups, dv, pool_rows), float("nan"), dtype=dtype, device=device)
+    token_pages = torch.full((pages, page_size, groups, dk + dv), float("nan"), dtype=dtype, device=device)   # a row: key | value
+    pool_pages = torch.full((pages, pool_rows, groups, dk + dv), float("nan"), dtype=dtype, device=device)
     qk_freq = (1.0 / (torch.tensor(base) ** (torch.arange(0, rot_dims, 2, dtype=torch.float32) / rot_dims))).to(device) if rot_dims else None
     v_freq = (1.0 / (torch.tensor(base) ** (torch.arange(0, dv, 2, dtype=torch.float32) / dv))).to(device)
     status = torch.zeros(1, dtype=torch.int32, device=device)
     as_int = lambda values: torch.tensor(values, dtype=torch.int32, device=device)
 
-    def step(portions):   # [(request, first position, count)]
+    def step(portions, on_tensor_cores=False):   # [(request, first position, count)]
         tokens = sum(count for _, _, count in portions)
         qkv = torch.cat([rows[r][first : first + count] for r, first, count in portions]).to(device)
         positions = as_int([p for _, first, count in portions for p in range(first, first + count)])
@@ -274,15 +273,21 @@ def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size,
         step_table = table[[r for r, _, _ in portions]].contiguous()
         q = torch.empty(tokens, heads * dk, dtype=dtype, device=device)
         shape = dict(num_heads=heads, num_groups=groups, head_dim=dk, value_dim=dv)
-        ops.pooled_rewrite(qkv, q, k_pages, v_pages, qk_freq=qk_freq, rotary_dim=rot_dims, value_freq=v_freq, positions=positions, token_segment=segment,
+        ops.pooled_rewrite(qkv, q, token_pages, qk_freq=qk_freq, rotary_dim=rot_dims, value_freq=v_freq, positions=positions, token_segment=segment,
                            block_table=step_table, write_kv=True, status=status, **shape)
-        ops.pooled_means(k_pages, v_pages, pk_pages, pv_pages, segment_length=as_int([count for _, _, count in portions]),
+        ops.pooled_means(token_pages, pool_pages, segment_length=as_int([count for _, _, count in portions]),
                          segment_context=as_int([first for _, first, _ in portions]), block_table=step_table, pool_table=step_table, segments=len(portions),
                          max_length=max(count for _, _, count in portions), num_groups=groups, head_dim=dk, value_dim=dv, pool=pool, status=status)
         out = torch.empty(tokens, heads * dv, dtype=dtype, device=device)
-        ops.pooled_attention_plain(q, k_pages, v_pages, pk_pages, pv_pages, out, positions=positions, token_segment=segment, block_table=step_table,
-                                   pool_table=step_table, scale=scale, softcap=cap, head_bias=bias.to(device), window=window, pool=pool, value_freq=v_freq,
-                                   status=status, **shape)
+        common = dict(positions=positions, token_segment=segment, block_table=step_table, pool_table=step_table, scale=scale, softcap=cap,
+                      head_bias=bias.to(device), window=window, pool=pool, value_freq=v_freq, status=status, **shape)
+        if on_tensor_cores:
+            size = ops.pooled_attention_tiling(heads, groups)[1]
+            starts = np.cumsum([0] + [count for _, _, count in portions[:-1]]).tolist()
+            tiles = [(first, min(size, start + count - first)) for start, (_, _, count) in zip(starts, portions) for first in range(start, start + count, size)]
+            ops.pooled_attention(q, token_pages, pool_pages, out, tiles=as_int([v for tile in tiles for v in tile]), num_tiles=len(tiles), **common)
+        else:
+            ops.pooled_attention_plain(q, token_pages, pool_pages, out, **common)
         return out
 
     for r, context in enumerate(contexts):
@@ -296,7 +301,7 @@ def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size,
             count = min(64, context - first)
             step([(r, first, count)])
             first += count
-    got = step([(r, context, count) for r, (context, count) in enumerate(zip(contexts, lengths))]).double().cpu()
+    got = step([(r, context, count) for r, (context, count) in enumerate(zip(contexts, lengths))], tensor_cores).double().cpu()
     assert int(status.item()) == 0
     offset = 0
     worst = 0.0
@@ -342,6 +347,22 @@ def test_pooled_attention_kernels_at_every_edge(dtype):
     ]
     for index, case in enumerate(cases):
         assert pooled_case(dtype, seed=20 + index, **case) < limit, case
+
+
+def test_pooled_attention_on_the_tensor_cores_at_every_edge():
+    """The tensor-core kernel over the same kinds of edges: heads of 16 to 128 channels with keys and values of different sizes, one
+    to eight query heads a K/V head, tiles that end inside a portion, windows and blocks that begin and end inside a tile of 64 rows."""
+    cases = [
+        dict(heads=4, groups=2, dk=16, dv=32, window=10, pool=4, rot_dims=8, page_size=16, contexts=[0, 9, 10, 13, 14, 31, 32, 47], lengths=[1] * 8, cap=20.0),
+        dict(heads=2, groups=2, dk=32, dv=16, window=16, pool=16, rot_dims=0, page_size=16, contexts=[15, 16, 31, 32, 33, 95], lengths=[1, 1, 1, 1, 1, 70], cap=0.0),
+        dict(heads=3, groups=1, dk=16, dv=16, window=7, pool=24, rot_dims=8, page_size=16, contexts=[22, 23, 29, 30, 31, 54], lengths=[1, 2, 1, 1, 5, 40], cap=5.0),
+        dict(heads=8, groups=1, dk=32, dv=32, window=1, pool=3, rot_dims=16, page_size=16, contexts=[0, 1, 2, 3, 4, 50], lengths=[1, 1, 1, 1, 33, 2], cap=30.0),
+        dict(heads=8, groups=8, dk=64, dv=48, window=96, pool=8, rot_dims=64, page_size=16, contexts=[0, 95, 103, 104, 200, 700], lengths=[130, 1, 1, 1, 17, 1], cap=30.0),
+        dict(heads=4, groups=1, dk=128, dv=128, window=70, pool=5, rot_dims=64, page_size=16, contexts=[0, 69, 330], lengths=[150, 3, 1], cap=30.0),
+        dict(heads=6, groups=3, dk=80, dv=96, window=130, pool=2, rot_dims=80, page_size=32, contexts=[0, 260], lengths=[200, 66], cap=12.0),
+    ]
+    for index, case in enumerate(cases):
+        assert pooled_case(torch.bfloat16, seed=40 + index, tensor_cores=True, **case) < 2e-2, case
 
 
 # ----------------------------------------------------------------------------- whole models
