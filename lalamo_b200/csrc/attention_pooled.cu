@@ -258,15 +258,16 @@ pooled_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pag
 }
 
 // ------------------------------------------------------------------------------------ tensor cores (bfloat16)
-// A CTA of four warps takes a tile of up to 16 * TB consecutive tokens of one portion and HB query heads of one K/V head
-// (HB * TB = 4: a warp is one head's 16 tokens).  Rows of the cache come 64 at a time through two cp.async stages, first the
+// A CTA of eight warps takes a tile of up to 16 * TB consecutive tokens of one portion and HB query heads of one K/V head
+// (HB * TB = 8, HB at most 4: a warp is one head's 16 tokens).  Rows of the cache come 64 at a time through two cp.async stages, first the
 // pooled blocks from block 0 on, then the positions from the multiple of 64 at or below the tile's first visible one: so the
 // tiles a query's keys fall into, and with them the order of its sums, depend on its position alone.  Rows that no query
 // of the CTA sees are zero-filled and never read.  S = Q K^T (m16n8k16, K straight from the rows), the weights in 32-bit with
 // a mask per element, P rounded to bfloat16 as the next product's A operand, O += P V with V through ldmatrix.trans from the
 // same rows.  At the end a head's sums are turned back by the query's position in registers (both channels of a pair lie in
-// one thread) and rounded once.
-constexpr int kPooledMmaKeys = 64, kPooledMmaWarps = 4;
+// one thread) and rounded once.  Where a launch has few CTAs (single decoded tokens), grid.z CTAs share out a tile's blocks of 64
+// rows; each writes its 32-bit sums, and `pooled_finish` adds them in the order of the shares, turns them back and rounds.
+constexpr int kPooledMmaKeys = 64, kPooledMmaWarps = 8;
 
 __device__ __forceinline__ void pooled_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -305,7 +306,8 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                             __nv_bfloat16* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ positions,
                             const int* __restrict__ token_segment, const int* __restrict__ block_table, const int* __restrict__ pool_table,
                             PooledLayout L, int heads, int head_block, float scale, float cap, const float* __restrict__ head_bias, int window, int pool,
-                            const float* __restrict__ v_freq, int v_interleaved, int* status) {
+                            const float* __restrict__ v_freq, int v_interleaved, int* status, float* __restrict__ partial, int total_rows) {
+    // partial (null if gridDim.z is 1): [share][row][head][dv], 32-bit sums not yet turned back
     extern __shared__ __align__(16) __nv_bfloat16 pooled_rows[];   // two stages of 64 rows of `pitch` elements
     const int row_width = L.dk + L.dv, pitch = row_width + 8;      // rows 16 bytes apart modulo 128: no bank is met twice
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -321,7 +323,9 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const int first_key = max(0, p_first - window + 1);
     const int pooled_tiles = (blocks_seen + kPooledMmaKeys - 1) / kPooledMmaKeys;
     const int first_token_tile = first_key / kPooledMmaKeys, token_tiles = p_last / kPooledMmaKeys - first_token_tile + 1;
-    const int num_tiles = pooled_tiles + token_tiles;
+    const int all_tiles = pooled_tiles + token_tiles;
+    const int tile_begin = static_cast<int>(static_cast<long long>(all_tiles) * blockIdx.z / gridDim.z);
+    const int tile_end = static_cast<int>(static_cast<long long>(all_tiles) * (blockIdx.z + 1) / gridDim.z);
     const int chunks = row_width / 8;   // 16-byte pieces of a row
     const size_t group_offset = static_cast<size_t>(group) * row_width, row_stride = static_cast<size_t>(L.groups) * row_width;
 
@@ -348,7 +352,7 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
-    load(0, 0);
+    if (tile_begin < tile_end) load(tile_begin & 1, tile_begin);
 
     // the warp's queries as A fragments, its rows' positions and what each of them sees
     const int row_g = token_block * 16 + g, row_g8 = row_g + 8;
@@ -374,9 +378,9 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 #pragma unroll
     for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
 
-    for (int tile = 0; tile < num_tiles; ++tile) {
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
         const int stage = tile & 1;
-        if (tile + 1 < num_tiles) {
+        if (tile + 1 < tile_end) {
             load(stage ^ 1, tile + 1);   // that stage was used up in the turn before (the barrier at its end)
             asm volatile("cp.async.wait_group 1;\n" ::: "memory");
         } else {
@@ -439,6 +443,17 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
         __syncthreads();   // the stage is refilled in the next turn
     }
     if (idle) return;
+    if (partial != nullptr) {
+#pragma unroll
+        for (int upper = 0; upper < 2; ++upper) {
+            if (!(upper == 0 ? live_g : live_g8)) continue;
+            float* destination = partial + ((static_cast<size_t>(blockIdx.z) * total_rows + first_row + (upper == 0 ? row_g : row_g8)) * heads + head) * L.dv;
+#pragma unroll
+            for (int n = 0; n < DV / 8; ++n)
+                if (8 * n < L.dv) *reinterpret_cast<float2*>(destination + 8 * n + 2 * t) = make_float2(o[n][2 * upper], o[n][2 * upper + 1]);
+        }
+        return;
+    }
     // turned back by the row's position, rounded once; o[n][0..1]: row g, channels 8 n + 2 t (+1); o[n][2..3]: row g + 8
     const int half_tiles = L.dv / 16;   // channel c and c + dv / 2 lie half_tiles tiles apart, in the same thread
 #pragma unroll
@@ -474,6 +489,31 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
             }
             *reinterpret_cast<uint32_t*>(destination + 8 * n + 2 * t) = pooled_pack(low, high);
         }
+    }
+}
+
+// grid (rows, heads), a thread per pair of channels: out = the shares' sums added in order, turned back by the row's position.
+__global__ void pooled_finish_kernel(const float* __restrict__ partial, int shares, __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
+                                     int total_rows, int heads, int dv, const float* __restrict__ v_freq, int v_interleaved) {
+    const int row = blockIdx.x, head = blockIdx.y;
+    const float p = static_cast<float>(positions[row]);
+    const size_t offset = (static_cast<size_t>(row) * heads + head) * dv, share_stride = static_cast<size_t>(total_rows) * heads * dv;
+    for (int pair = threadIdx.x; pair < dv / 2; pair += blockDim.x) {
+        const int first = v_interleaved ? 2 * pair : pair, second = v_interleaved ? 2 * pair + 1 : pair + dv / 2;
+        float a = 0.0f, b = 0.0f;
+        for (int share = 0; share < shares; ++share) {
+            a += partial[share * share_stride + offset + first];
+            b += partial[share * share_stride + offset + second];
+        }
+        if (v_freq != nullptr) {
+            float sine, cosine;
+            sincosf(p * v_freq[pair], &sine, &cosine);
+            const float turned = a * cosine + b * sine;
+            b = b * cosine - a * sine;
+            a = turned;
+        }
+        out[offset + first] = __float2bfloat16_rn(a);
+        out[offset + second] = __float2bfloat16_rn(b);
     }
 }
 
@@ -527,16 +567,20 @@ int lb_pooled_attention_plain(const void* q, const void* pages, const void* pool
     return LB_LAUNCH_RESULT();
 }
 
-// head_block: the query heads of a K/V head that one CTA takes (1 to 4; its tiles have 64 / head_block tokens at most... 16 * (4 / head_block)).
+// head_block: the query heads of a K/V head that one CTA takes (1 to 4; its tiles have 16 * (8 / head_block) tokens at most).  shares > 1:
+// that many CTAs share out a tile's rows; `partial` then holds shares x total_rows x heads x dv floats.
 int lb_pooled_attention_mma(const void* q, const void* pages, const void* pooled_pages, void* out, const int* tiles, int num_tiles, const int* positions,
                             const int* token_segment, const int* block_table, const int* pool_table, int heads, int groups, int dk, int dv, int page_size,
                             int num_pages, int max_blocks, int pool_rows, int pool_pages, int pool_max_blocks, int head_block, float scale, float cap,
-                            const float* head_bias, int window, int pool, const float* v_freq, int v_interleaved, int* status, cudaStream_t stream) {
+                            const float* head_bias, int window, int pool, const float* v_freq, int v_interleaved, int* status, cudaStream_t stream, int shares,
+                            float* partial, int total_rows) {
     if (num_tiles == 0) return 0;
+    if (shares < 1 || shares > 64 || (shares > 1 && partial == nullptr)) return -2;
+    if (shares == 1) partial = nullptr;
     if (heads % groups != 0 || dk % 16 != 0 || dv % 16 != 0 || dk < 16 || dv < 16 || dk > 128 || dv > 128 || window < 1 || pool < 0 || head_block < 1 || head_block > 4) return -2;
     lb::PooledLayout L{page_size, num_pages, max_blocks, pool_rows > 0 ? pool_rows : 1, pool_pages, pool_max_blocks, groups, dk, dv};
     const int per_group = heads / groups;
-    const dim3 grid(num_tiles, groups * ((per_group + head_block - 1) / head_block));
+    const dim3 grid(num_tiles, groups * ((per_group + head_block - 1) / head_block), shares);
     const size_t shared = 2 * static_cast<size_t>(lb::kPooledMmaKeys) * (dk + dv + 8) * sizeof(__nv_bfloat16);
     const auto* q16 = static_cast<const __nv_bfloat16*>(q);
     const auto* pages16 = static_cast<const __nv_bfloat16*>(pages);
@@ -547,14 +591,16 @@ int lb_pooled_attention_mma(const void* q, const void* pages, const void* pooled
         lb::allow_shared_memory(once, lb::pooled_attention_mma_kernel<64, 64>, 2 * lb::kPooledMmaKeys * (128 + 8) * 2);
         lb::pooled_attention_mma_kernel<64, 64><<<grid, 32 * lb::kPooledMmaWarps, shared, stream>>>(
             q16, pages16, pooled16, out16, tiles, positions, token_segment, block_table, pool_table, L, heads, head_block, scale, cap, head_bias, window, pool, v_freq,
-            v_interleaved, status);
+            v_interleaved, status, partial, total_rows);
     } else {
         static lb::OncePerDevice once;
         lb::allow_shared_memory(once, lb::pooled_attention_mma_kernel<128, 128>, 2 * lb::kPooledMmaKeys * (256 + 8) * 2);
         lb::pooled_attention_mma_kernel<128, 128><<<grid, 32 * lb::kPooledMmaWarps, shared, stream>>>(
             q16, pages16, pooled16, out16, tiles, positions, token_segment, block_table, pool_table, L, heads, head_block, scale, cap, head_bias, window, pool, v_freq,
-            v_interleaved, status);
+            v_interleaved, status, partial, total_rows);
     }
+    if (shares > 1)
+        lb::pooled_finish_kernel<<<dim3(total_rows, heads), 64, 0, stream>>>(partial, shares, out16, positions, total_rows, heads, dv, v_freq, v_interleaved);
     return LB_LAUNCH_RESULT();
 }
 

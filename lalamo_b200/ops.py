@@ -1332,7 +1332,8 @@ def branch_norms_accumulate(residual: torch.Tensor, terms: list, eps: float) -> 
 def linear_attention(proj: torch.Tensor, matrix_state: torch.Tensor, *, num_heads: int, key_dim: int, value_dim: int, decay_logits: torch.Tensor | None = None,
                      decay_bias: torch.Tensor | None = None, fixed_decay: torch.Tensor | None = None, tau: float = 1.0, query_scale: float = 1.0,
                      key_scale: float = 1.0, norm_weight: torch.Tensor, norm_eps: float, gate_offset: int, gate_activation: str = "silu",
-                     segment_start: torch.Tensor, segment_length: torch.Tensor, segment_slot: torch.Tensor, segments: int, status: torch.Tensor) -> torch.Tensor:
+                     segment_start: torch.Tensor, segment_length: torch.Tensor, segment_slot: torch.Tensor, segments: int, status: torch.Tensor,
+                     chunk_plan: dict | None = None) -> torch.Tensor:
     """Linear attention ``S_t = diag(a_t) S_(t-1) + k_t v_t^T; o_t = S_t^T q_t`` over the step's portions, from each request's state
     slot and back into it, then the per-head RMS norm of the read-out (times ``norm_weight``) times the gate.
 
@@ -1340,7 +1341,9 @@ def linear_attention(proj: torch.Tensor, matrix_state: torch.Tensor, *, num_head
     (``heads x value_dim``) and, from column ``gate_offset`` on, the gate's logits.  The decay is ``fixed_decay`` (32-bit, one per
     head) or ``sigmoid(decay_logits + decay_bias) ** (1 / tau)`` (``decay_logits`` ``[tokens, heads * key_dim]`` in the
     activation type, the bias 32-bit).  ``matrix_state`` is ``[slots, heads, key_dim, value_dim]`` in 32-bit.  Returns
-    ``[tokens, heads * value_dim]`` in the activation type."""
+    ``[tokens, heads * value_dim]`` in the activation type.  ``chunk_plan`` (see :func:`gated_delta_chunk_plan`) lets long portions run as
+    chunks side by side, as the gated delta rule's do: the recurrence is linear in the state, and the chunks' further columns carry
+    their decays' products."""
     _check(proj, "proj")
     _check(matrix_state, "matrix_state", torch.float32)
     _check(norm_weight, "norm_weight", torch.float32)
@@ -1383,11 +1386,30 @@ def linear_attention(proj: torch.Tensor, matrix_state: torch.Tensor, *, num_head
                                            _ptr(decay), c_int(tokens), c_int(num_heads), c_int(key_dim), c_int(value_dim), c_int(dtype_code(proj.dtype)), _stream())
     _done(code, "linear_attention_prepare")
     read_out = torch.empty(tokens, num_heads, value_dim, dtype=torch.float32, device=device)
-    # the scan of the gated delta rule without its correction (no beta)
-    code = lib.lb_gdr_scan(_ptr(q), _ptr(k), _ptr(decay), _ptr(v), _ptr(None), _ptr(matrix_state), _ptr(read_out), _ptr(segment_start), _ptr(segment_length),
-                           _ptr(segment_slot), c_int(segments), c_int(num_heads), c_int(num_heads), c_int(key_dim), c_int(value_dim), c_int(num_slots),
-                           _ptr(status), _stream(), _ptr(None), c_int(value_dim))
-    _done(code, "linear_attention_scan")
+    # the scan of the gated delta rule without its correction (no beta), long portions in chunks where that pays
+    direct_list, num_direct = None, segments
+    if chunk_plan is not None and chunk_plan["num_chunks"] > 0 and gated_delta_chunks_pay(key_dim, value_dim):
+        num_chunks, num_long = chunk_plan["num_chunks"], chunk_plan["num_long"]
+        wide_dim = value_dim + key_dim
+        wide = torch.empty(tokens, num_heads, wide_dim, dtype=torch.float32, device=device)
+        chunk_state = torch.empty(num_chunks, num_heads, key_dim, wide_dim, dtype=torch.float32, device=device)
+        chunk_in = torch.empty(num_chunks, num_heads, key_dim, value_dim, dtype=torch.float32, device=device)
+        _done(lib.lb_gdr_chunk_init(_ptr(chunk_state), c_int(num_chunks), c_int(num_heads), c_int(key_dim), c_int(value_dim), _stream()), "gdr_chunk_init")
+        code = lib.lb_gdr_scan(_ptr(q), _ptr(k), _ptr(decay), _ptr(v), _ptr(None), _ptr(chunk_state), _ptr(wide), _ptr(chunk_plan["chunk_start"]),
+                               _ptr(chunk_plan["chunk_length"]), _ptr(chunk_plan["chunk_slot"]), c_int(num_chunks), c_int(num_heads), c_int(num_heads),
+                               c_int(key_dim), c_int(wide_dim), c_int(num_chunks), _ptr(status), _stream(), _ptr(None), c_int(value_dim))
+        _done(code, "linear_attention_scan (chunks)")
+        code = lib.lb_gdr_chunk_finish(_ptr(chunk_state), _ptr(chunk_in), _ptr(matrix_state), _ptr(wide), _ptr(read_out), _ptr(chunk_plan["long_table"]),
+                                       c_int(num_long), _ptr(segment_slot), _ptr(chunk_plan["chunk_start"]), _ptr(chunk_plan["chunk_length"]), c_int(num_chunks),
+                                       c_int(chunk_plan.get("chunk_tokens", GDR_CHUNK_TOKENS)), c_int(num_heads), c_int(key_dim), c_int(value_dim), c_int(num_slots),
+                                       _stream())
+        _done(code, "gdr_chunk_finish", 2)
+        direct_list, num_direct = chunk_plan["direct"], chunk_plan["num_direct"]
+    if num_direct > 0:
+        code = lib.lb_gdr_scan(_ptr(q), _ptr(k), _ptr(decay), _ptr(v), _ptr(None), _ptr(matrix_state), _ptr(read_out), _ptr(segment_start), _ptr(segment_length),
+                               _ptr(segment_slot), c_int(num_direct), c_int(num_heads), c_int(num_heads), c_int(key_dim), c_int(value_dim), c_int(num_slots),
+                               _ptr(status), _stream(), _ptr(direct_list), c_int(value_dim))
+        _done(code, "linear_attention_scan")
     out = torch.empty(tokens, num_heads * value_dim, dtype=proj.dtype, device=device)
     code = lib.lb_gdr_output(_ptr(read_out), _ptr(proj), c_int(proj.shape[1]), c_int(gate_offset), _ptr(norm_weight), _ptr(out), c_int(tokens),
                              c_int(num_heads), c_int(value_dim), c_float(norm_eps), c_int(dtype_code(proj.dtype)), _stream(), c_int(1 if gate_activation == "silu" else 0))
@@ -1461,9 +1483,18 @@ POOLED_MMA_HEADS = 4  # query heads of one K/V head that a CTA of the tensor-cor
 
 
 def pooled_attention_tiling(num_heads: int, num_groups: int) -> tuple[int, int]:
-    """``(query heads of a K/V head per CTA, tokens per tile)`` of the tensor-core kernel: a CTA's four warps are one head's 16 tokens each."""
+    """``(query heads of a K/V head per CTA, tokens per tile)`` of the tensor-core kernel: a CTA's eight warps are one head's 16 tokens each."""
     head_block = min(num_heads // num_groups, POOLED_MMA_HEADS)
-    return head_block, 16 * (4 // head_block)
+    return head_block, 16 * (8 // head_block)
+
+
+def pooled_attention_shares(num_tiles: int, num_heads: int, num_groups: int, sms: int | None = None) -> int:
+    """How many CTAs share out a tile's rows of the cache: one where the launch fills the multiprocessors anyway, else enough for
+    two CTAs a multiprocessor, 16 at most.  It depends on the launch's shape alone (a recorded step keeps it)."""
+    head_block, _ = pooled_attention_tiling(num_heads, num_groups)
+    ctas = num_tiles * num_groups * -(-(num_heads // num_groups) // head_block)
+    sms = sms or sm_count()
+    return 1 if ctas >= sms else max(1, min(16, -(-2 * sms // ctas)))
 
 
 def pooled_attention_supported(dtype: torch.dtype, head_dim: int, value_dim: int) -> bool:
@@ -1516,13 +1547,15 @@ def pooled_attention_plain(q: torch.Tensor, pages: torch.Tensor, pool_pages: tor
     _done(code, "pooled_attention_plain")
 
 
-def pooled_attention(q: torch.Tensor, pages: torch.Tensor, pool_pages: torch.Tensor | None, out: torch.Tensor, *, tiles: torch.Tensor, num_tiles: int,
+def pooled_attention(q: torch.Tensor, pages: torch.Tensor, pool_pages: torch.Tensor | None, out: torch.Tensor, *, tiles: torch.Tensor, num_tiles: int, shares: int | None = None,
                      positions: torch.Tensor, token_segment: torch.Tensor, block_table: torch.Tensor, pool_table: torch.Tensor | None, num_heads: int,
                      num_groups: int, head_dim: int, value_dim: int, scale: float, softcap: float, head_bias: torch.Tensor | None, window: int, pool: int,
                      value_freq: torch.Tensor | None, interleaved: bool = False, status: torch.Tensor) -> None:
     """The same attention on the tensor cores (bfloat16; see :func:`pooled_attention_supported`).  ``tiles``: int32 ``(first row, count)``
     per tile of consecutive tokens of one portion, at most :func:`pooled_attention_tiling`'s tokens each.  Weights in 32-bit (the cap's
-    tanh and the sigmoid's exponential by the fast units), rounded to bfloat16 for the product with the values; sums in 32-bit."""
+    tanh and the sigmoid's exponential by the fast units), rounded to bfloat16 for the product with the values; sums in 32-bit.  Launches
+    of few CTAs share out every tile's rows of the cache over several CTAs (:func:`pooled_attention_shares`), whose 32-bit sums a second
+    kernel adds in order."""
     tokens, (count, page_size, max_blocks), (pool_count, pool_rows, pool_blocks) = _pooled_arguments(
         q, pages, pool_pages, out, positions, token_segment, block_table, pool_table, num_heads, num_groups, head_dim, value_dim, head_bias, window, pool,
         value_freq, "pooled_attention")
@@ -1532,12 +1565,17 @@ def pooled_attention(q: torch.Tensor, pages: torch.Tensor, pool_pages: torch.Ten
     if tiles.numel() < 2 * num_tiles:
         raise KernelError("pooled_attention: fewer tile records than tiles")
     head_block, _ = pooled_attention_tiling(num_heads, num_groups)
+    if shares is None:
+        shares = pooled_attention_shares(num_tiles, num_heads, num_groups)
+    if not 1 <= shares <= 64:
+        raise KernelError("pooled_attention: 1 to 64 shares")
+    partial = torch.empty(shares, tokens, num_heads * value_dim, dtype=torch.float32, device=q.device) if shares > 1 else None
     code = _lib().lb_pooled_attention_mma(_ptr(q), _ptr(pages), _ptr(pool_pages if pool else None), _ptr(out), _ptr(tiles), c_int(num_tiles), _ptr(positions),
                                           _ptr(token_segment), _ptr(block_table), _ptr(pool_table if pool else None), c_int(num_heads), c_int(num_groups),
                                           c_int(head_dim), c_int(value_dim), c_int(page_size), c_int(count), c_int(max_blocks), c_int(pool_rows), c_int(pool_count),
                                           c_int(pool_blocks), c_int(head_block), c_float(scale), c_float(softcap), _ptr(head_bias), c_int(window), c_int(pool),
-                                          _ptr(value_freq), c_int(1 if interleaved else 0), _ptr(status), _stream())
-    _done(code, "pooled_attention")
+                                          _ptr(value_freq), c_int(1 if interleaved else 0), _ptr(status), _stream(), c_int(shares), _ptr(partial), c_int(tokens))
+    _done(code, "pooled_attention", 2 if shares > 1 else 1)
 
 
 # ------------------------------------------------------------------------------ sampling

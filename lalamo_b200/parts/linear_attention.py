@@ -12,11 +12,12 @@ from __future__ import annotations
 
 from typing import Mapping
 
+import numpy as np
 import torch
 
 from .. import ops
 from ..config.plan import LinearAttentionSpec
-from .base import CacheNeed, Mixer, Runtime, SlotStateNeed, SlotStateView, StepInputs, TensorDecl, register_part
+from .base import CacheNeed, HostSegments, Mixer, Runtime, SlotStateNeed, SlotStateView, StepInputs, TensorDecl, register_part
 
 __all__ = ["LinearAttention"]
 
@@ -86,6 +87,16 @@ class LinearAttention(Mixer):
         spec = self.spec
         return SlotStateNeed(shape=(spec.num_heads, spec.key_dim, spec.value_dim), dtype=torch.float32)
 
+    # Long portions run in chunks side by side (the plan the gated delta rule's layers make, shared with them): which rows belong
+    # to which chunk depends on the portions' lengths only.
+    step_plan_uses_context = False
+
+    def step_plan_key(self) -> object:
+        return ("gated_delta", ops.GDR_CHUNK_TOKENS, ops.GDR_LONG_PORTION)
+
+    def plan_step(self, segments: HostSegments) -> dict[str, np.ndarray]:
+        return ops.gated_delta_chunk_plan(segments.start, segments.length)
+
     can_accumulate = True
 
     def forward(self, x: torch.Tensor, step: StepInputs, cache: SlotStateView, residual: torch.Tensor | None = None) -> torch.Tensor | None:  # type: ignore[override]
@@ -93,6 +104,8 @@ class LinearAttention(Mixer):
         if not cache.owns:
             raise ValueError("a linear-attention layer cannot read another layer's state")
         status = self.runtime.status
+        lists, host_lists = step.plan_of(self)
+        chunk_plan = dict(lists, num_chunks=host_lists["chunk_start"].size, num_long=host_lists["long_table"].size // 3, num_direct=host_lists["direct"].size)
         proj = ops.linear(x, self.in_proj, status=status)
         logits = None
         if self.decay_down is not None:
@@ -118,6 +131,7 @@ class LinearAttention(Mixer):
             segment_slot=cache.segment_slot,
             segments=step.segments,
             status=status,
+            chunk_plan=chunk_plan,
         )
         if residual is not None:
             return ops.linear_accumulate(read_out, self.out_proj, residual, status=status)

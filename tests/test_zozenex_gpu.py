@@ -239,11 +239,11 @@ def test_router_with_a_choice_bias_and_experts_without_a_gate():
     assert torch.allclose(stream.double().cpu(), want + scores[:, experts : experts + 1] * shared.double(), rtol=2e-2, atol=2e-2)
 
 
-def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size, contexts, lengths, cap, seed, tensor_cores=False):
+def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size, contexts, lengths, cap, seed, tensor_cores=False, shares=None):
     """One step of the pooled attention's kernels over requests that hold ``contexts`` tokens already and bring ``lengths`` more (the
     earlier tokens go through the same kernels, one request a step, in uneven portions), against the plain attention over each
     request's whole sequence.  Pages are handed out in a scattered order.  ``tensor_cores``: the last step's attention on the tensor-core
-    kernel, in tiles of consecutive tokens."""
+    kernel, in tiles of consecutive tokens (``shares``: so many CTAs share out a tile's rows; left out, the launch's shape decides)."""
     from lalamo_b200 import ops
 
     device = torch.device("cuda")
@@ -285,7 +285,7 @@ def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size,
             size = ops.pooled_attention_tiling(heads, groups)[1]
             starts = np.cumsum([0] + [count for _, _, count in portions[:-1]]).tolist()
             tiles = [(first, min(size, start + count - first)) for start, (_, _, count) in zip(starts, portions) for first in range(start, start + count, size)]
-            ops.pooled_attention(q, token_pages, pool_pages, out, tiles=as_int([v for tile in tiles for v in tile]), num_tiles=len(tiles), **common)
+            ops.pooled_attention(q, token_pages, pool_pages, out, tiles=as_int([v for tile in tiles for v in tile]), num_tiles=len(tiles), shares=shares, **common)
         else:
             ops.pooled_attention_plain(q, token_pages, pool_pages, out, **common)
         return out
@@ -362,7 +362,8 @@ def test_pooled_attention_on_the_tensor_cores_at_every_edge():
         dict(heads=6, groups=3, dk=80, dv=96, window=130, pool=2, rot_dims=80, page_size=32, contexts=[0, 260], lengths=[200, 66], cap=12.0),
     ]
     for index, case in enumerate(cases):
-        assert pooled_case(torch.bfloat16, seed=40 + index, tensor_cores=True, **case) < 2e-2, case
+        for shares in (1, None, 5):   # every tile's rows in one CTA, as the launch's shape decides, and shared out over five
+            assert pooled_case(torch.bfloat16, seed=40 + index, tensor_cores=True, shares=shares, **case) < 2e-2, (case, shares)
 
 
 # ----------------------------------------------------------------------------- whole models
@@ -470,7 +471,8 @@ def test_long_portions_beside_a_short_request(models, name, dtype):
     folder, weights = models[name]
     config = CONFIGS[name]
     requests = {"a": tokens_for(config, 1300, 41), "b": tokens_for(config, 30, 42)}
-    schedule = [[("a", 700), ("b", 5)], [("a", 1), ("b", 20)], [("a", 590), ("b", 1)], [("b", 4), ("a", 9)]]
+    # 900 tokens at once: long enough for a recurrence to run as chunks side by side where its head shape makes that pay
+    schedule = [[("a", 900), ("b", 5)], [("a", 1), ("b", 20)], [("a", 390), ("b", 1)], [("b", 4), ("a", 9)]]
     compare(load_engine(folder, dtype, max_tokens=2048, config=config), config, weights, requests, schedule, dtype)
 
 
