@@ -287,11 +287,41 @@ __device__ __forceinline__ void pooled_copy_16(void* shared_destination, const v
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(destination), "l"(global_source), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ float pooled_tanh(float x) {
+// The weight of a score in as few instructions as it takes, through the fast base-2 exponential and reciprocal (relative errors
+// near 2^-22; the approximate tanh instruction's absolute error of 2^-11, times a cap of tens, would move a score by more than
+// bfloat16 rounding does):  tanh(x) = 1 - 2 r with r = 1 / (1 + 2^(2 x log2 e)),  sigmoid(y) = 1 / (1 + 2^(-y log2 e)).
+__device__ __forceinline__ float pooled_exp2(float x) {
     float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float pooled_reciprocal(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+struct PooledWeight {
+    float to_exponent, slope, offset;   // capped: e = 2^(s to_exponent), r = 1 / (1 + e), w = 1 / (1 + 2^(r slope + offset)); plain: w = 1 / (1 + 2^(s slope + offset))
+    bool capped;
+    __device__ __forceinline__ PooledWeight(float scale, float cap, float bias) {
+        constexpr float kLog2e = 1.4426950408889634f;
+        capped = cap > 0.0f;
+        if (capped) {
+            // score = cap (1 - 2 r);  -(score + bias) log2 e = r (2 cap log2 e) - (cap + bias) log2 e
+            to_exponent = 2.0f * scale / cap * kLog2e;
+            slope = 2.0f * cap * kLog2e;
+            offset = -(cap + bias) * kLog2e;
+        } else {
+            to_exponent = 0.0f;
+            slope = -scale * kLog2e;
+            offset = -bias * kLog2e;
+        }
+    }
+    __device__ __forceinline__ float operator()(float dot) const {
+        const float x = capped ? pooled_reciprocal(1.0f + pooled_exp2(dot * to_exponent)) : dot;
+        return pooled_reciprocal(1.0f + pooled_exp2(fmaf(x, slope, offset)));
+    }
+};
 
 __device__ __forceinline__ uint32_t pooled_pack(float low, float high) {
     const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
@@ -329,28 +359,29 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const int chunks = row_width / 8;   // 16-byte pieces of a row
     const size_t group_offset = static_cast<size_t>(group) * row_width, row_stride = static_cast<size_t>(L.groups) * row_width;
 
-    auto load = [&](int stage, int tile) {
-        __nv_bfloat16* destination = pooled_rows + static_cast<size_t>(stage) * kPooledMmaKeys * pitch;
+    // Four threads copy a row, 16 bytes each and turn; the row's page is looked up a tile ahead (while the tile before is worked on),
+    // so that no copy waits for its block-table entry.
+    const int load_row = threadIdx.x >> 2, load_part = threadIdx.x & 3;
+    auto lookup = [&](int tile) -> int {   // the page of this thread's row of the tile, -1 if the row is not to be read
+        if (tile >= tile_end) return -1;
         const bool pooled = tile < pooled_tiles;
-        const int base = pooled ? tile * kPooledMmaKeys : (first_token_tile + tile - pooled_tiles) * kPooledMmaKeys;
-        for (int index = threadIdx.x; index < kPooledMmaKeys * chunks; index += blockDim.x) {
-            const int row = index / chunks, chunk = index - row * chunks;
-            const int where = base + row;
-            bool valid = pooled ? where < blocks_seen : (where >= first_key && where <= p_last);
-            const __nv_bfloat16* source = pages;
-            if (valid) {
-                const int page = pooled ? pooled_page(pool_table, L, segment, where) : token_page(block_table, L, segment, where);
-                if (page < 0) {
-                    report_error(status, kBadPage);
-                    valid = false;
-                } else {
-                    const int per_page = pooled ? L.pool_rows : L.page_size;
-                    source = (pooled ? pooled_pages : pages) + (static_cast<size_t>(page) * per_page + where % per_page) * row_stride + group_offset + 8 * chunk;
-                }
-            }
-            pooled_copy_16(destination + static_cast<size_t>(row) * pitch + 8 * chunk, source, valid);
-        }
+        const int where = (pooled ? tile * kPooledMmaKeys : (first_token_tile + tile - pooled_tiles) * kPooledMmaKeys) + load_row;
+        if (!(pooled ? where < blocks_seen : (where >= first_key && where <= p_last))) return -1;
+        const int page = pooled ? pooled_page(pool_table, L, segment, where) : token_page(block_table, L, segment, where);
+        if (page < 0) report_error(status, kBadPage);
+        return page;
+    };
+    int page_ahead = lookup(tile_begin);
+    auto load = [&](int stage, int tile) {
+        __nv_bfloat16* destination = pooled_rows + (static_cast<size_t>(stage) * kPooledMmaKeys + load_row) * pitch;
+        const bool pooled = tile < pooled_tiles;
+        const int where = (pooled ? tile * kPooledMmaKeys : (first_token_tile + tile - pooled_tiles) * kPooledMmaKeys) + load_row;
+        const int page = page_ahead;
+        const int per_page = pooled ? L.pool_rows : L.page_size;
+        const __nv_bfloat16* source = (pooled ? pooled_pages : pages) + (page < 0 ? 0 : (static_cast<size_t>(page) * per_page + where % per_page) * row_stride + group_offset);
+        for (int chunk = load_part; chunk < chunks; chunk += 4) pooled_copy_16(destination + 8 * chunk, source + 8 * chunk, page >= 0);
         asm volatile("cp.async.commit_group;\n" ::: "memory");
+        page_ahead = lookup(tile + 1);
     };
     if (tile_begin < tile_end) load(tile_begin & 1, tile_begin);
 
@@ -372,8 +403,7 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
             q_a[ks][3] = live_g8 && in_k ? *reinterpret_cast<const uint32_t*>(q_g8 + 16 * ks + 8 + 2 * t) : 0u;
         }
     }
-    const float bias = head_bias != nullptr ? head_bias[head] : 0.0f;
-    const float inverse_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
+    const PooledWeight weight_of(scale, cap, head_bias != nullptr ? head_bias[head] : 0.0f);
     float o[DV / 8][4];
 #pragma unroll
     for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
@@ -407,17 +437,27 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                     }
                 }
             }
+            // a tile all of whose rows every one of the warp's 16 queries sees needs no mask (all its queries exist, then)
+            const bool all_seen = token_block * 16 + 15 < count &&
+                                  (pooled ? base + kPooledMmaKeys <= (pool > 0 ? max(0, p_low - window + 1) / pool : 0)
+                                          : (base + kPooledMmaKeys - 1 <= p_low && base + window > p_low + 15));
+            if (all_seen) {
 #pragma unroll
-            for (int n = 0; n < kPooledMmaKeys / 8; ++n) {
+                for (int n = 0; n < kPooledMmaKeys / 8; ++n) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int where = base + 8 * n + 2 * t + (e & 1);
-                    const bool upper = e < 2;   // row g; else row g + 8
-                    const bool seen = pooled ? where < (upper ? seen_g : seen_g8)
-                                             : (upper ? (live_g && where <= p_g && where + window > p_g) : (live_g8 && where <= p_g8 && where + window > p_g8));
-                    float score = sc[n][e] * scale;
-                    if (cap > 0.0f) score = cap * pooled_tanh(score * inverse_cap);
-                    sc[n][e] = seen ? __fdividef(1.0f, 1.0f + __expf(-(score + bias))) : 0.0f;
+                    for (int e = 0; e < 4; ++e) sc[n][e] = weight_of(sc[n][e]);
+                }
+            } else {
+#pragma unroll
+                for (int n = 0; n < kPooledMmaKeys / 8; ++n) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int where = base + 8 * n + 2 * t + (e & 1);
+                        const bool upper = e < 2;   // row g; else row g + 8
+                        const bool seen = pooled ? where < (upper ? seen_g : seen_g8)
+                                                 : (upper ? (live_g && where <= p_g && where + window > p_g) : (live_g8 && where <= p_g8 && where + window > p_g8));
+                        sc[n][e] = seen ? weight_of(sc[n][e]) : 0.0f;
+                    }
                 }
             }
 #pragma unroll
@@ -492,13 +532,15 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     }
 }
 
-// grid (rows, heads), a thread per pair of channels: out = the shares' sums added in order, turned back by the row's position.
+// grid (rows), a thread per head and pair of channels: out = the shares' sums added in order, turned back by the row's position.
 __global__ void pooled_finish_kernel(const float* __restrict__ partial, int shares, __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
                                      int total_rows, int heads, int dv, const float* __restrict__ v_freq, int v_interleaved) {
-    const int row = blockIdx.x, head = blockIdx.y;
+    const int row = blockIdx.x;
     const float p = static_cast<float>(positions[row]);
-    const size_t offset = (static_cast<size_t>(row) * heads + head) * dv, share_stride = static_cast<size_t>(total_rows) * heads * dv;
-    for (int pair = threadIdx.x; pair < dv / 2; pair += blockDim.x) {
+    const size_t share_stride = static_cast<size_t>(total_rows) * heads * dv;
+    for (int index = threadIdx.x; index < heads * (dv / 2); index += blockDim.x) {
+        const int head = index / (dv / 2), pair = index - head * (dv / 2);
+        const size_t offset = (static_cast<size_t>(row) * heads + head) * dv;
         const int first = v_interleaved ? 2 * pair : pair, second = v_interleaved ? 2 * pair + 1 : pair + dv / 2;
         float a = 0.0f, b = 0.0f;
         for (int share = 0; share < shares; ++share) {
@@ -600,7 +642,7 @@ int lb_pooled_attention_mma(const void* q, const void* pages, const void* pooled
             v_interleaved, status, partial, total_rows);
     }
     if (shares > 1)
-        lb::pooled_finish_kernel<<<dim3(total_rows, heads), 64, 0, stream>>>(partial, shares, out16, positions, total_rows, heads, dv, v_freq, v_interleaved);
+        lb::pooled_finish_kernel<<<total_rows, 256, 0, stream>>>(partial, shares, out16, positions, total_rows, heads, dv, v_freq, v_interleaved);
     return LB_LAUNCH_RESULT();
 }
 

@@ -1489,12 +1489,12 @@ def pooled_attention_tiling(num_heads: int, num_groups: int) -> tuple[int, int]:
 
 
 def pooled_attention_shares(num_tiles: int, num_heads: int, num_groups: int, sms: int | None = None) -> int:
-    """How many CTAs share out a tile's rows of the cache: one where the launch fills the multiprocessors anyway, else enough for
-    two CTAs a multiprocessor, 16 at most.  It depends on the launch's shape alone (a recorded step keeps it)."""
+    """How many CTAs share out a tile's rows of the cache: one where the launch has four CTAs a multiprocessor anyway, else enough
+    for that many, 16 at most.  It depends on the launch's shape alone (a recorded step keeps it)."""
     head_block, _ = pooled_attention_tiling(num_heads, num_groups)
     ctas = num_tiles * num_groups * -(-(num_heads // num_groups) // head_block)
     sms = sms or sm_count()
-    return 1 if ctas >= sms else max(1, min(16, -(-2 * sms // ctas)))
+    return 1 if ctas >= 4 * sms else max(1, min(16, -(-4 * sms // ctas)))
 
 
 def pooled_attention_supported(dtype: torch.dtype, head_dim: int, value_dim: int) -> bool:
@@ -1553,7 +1553,7 @@ def pooled_attention(q: torch.Tensor, pages: torch.Tensor, pool_pages: torch.Ten
                      value_freq: torch.Tensor | None, interleaved: bool = False, status: torch.Tensor) -> None:
     """The same attention on the tensor cores (bfloat16; see :func:`pooled_attention_supported`).  ``tiles``: int32 ``(first row, count)``
     per tile of consecutive tokens of one portion, at most :func:`pooled_attention_tiling`'s tokens each.  Weights in 32-bit (the cap's
-    tanh and the sigmoid's exponential by the fast units), rounded to bfloat16 for the product with the values; sums in 32-bit.  Launches
+    tanh and the sigmoid through the fast exponential and reciprocal), rounded to bfloat16 for the product with the values; sums in 32-bit.  Launches
     of few CTAs share out every tile's rows of the cache over several CTAs (:func:`pooled_attention_shares`), whose 32-bit sums a second
     kernel adds in order."""
     tokens, (count, page_size, max_blocks), (pool_count, pool_rows, pool_blocks) = _pooled_arguments(
