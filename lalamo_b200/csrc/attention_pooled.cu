@@ -259,7 +259,7 @@ pooled_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pag
 
 // ------------------------------------------------------------------------------------ tensor cores (bfloat16)
 // A CTA of eight warps takes a tile of up to 16 * TB consecutive tokens of one portion and HB query heads of one K/V head
-// (HB * TB = 8, HB at most 4: a warp is one head's 16 tokens).  Rows of the cache come 64 at a time through two cp.async stages, first the
+// (HB * TB = 8, HB at most 4: a warp is one head's 16 tokens).  Rows of the cache come 64 at a time through four cp.async stages, first the
 // pooled blocks from block 0 on, then the positions from the multiple of 64 at or below the tile's first visible one: so the
 // tiles a query's keys fall into, and with them the order of its sums, depend on its position alone.  Rows that no query
 // of the CTA sees are zero-filled and never read.  S = Q K^T (m16n8k16, K straight from the rows), the weights in 32-bit with
@@ -267,7 +267,7 @@ pooled_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pag
 // same rows.  At the end a head's sums are turned back by the query's position in registers (both channels of a pair lie in
 // one thread) and rounded once.  Where a launch has few CTAs (single decoded tokens), grid.z CTAs share out a tile's blocks of 64
 // rows; each writes its 32-bit sums, and `pooled_finish` adds them in the order of the shares, turns them back and rounds.
-constexpr int kPooledMmaKeys = 64, kPooledMmaWarps = 8;
+constexpr int kPooledMmaKeys = 64, kPooledMmaWarps = 8, kPooledMmaStages = 4;   // three tiles on their way while one is worked on
 
 __device__ __forceinline__ void pooled_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -338,7 +338,7 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                             PooledLayout L, int heads, int head_block, float scale, float cap, const float* __restrict__ head_bias, int window, int pool,
                             const float* __restrict__ v_freq, int v_interleaved, int* status, float* __restrict__ partial, int total_rows) {
     // partial (null if gridDim.z is 1): [share][row][head][dv], 32-bit sums not yet turned back
-    extern __shared__ __align__(16) __nv_bfloat16 pooled_rows[];   // two stages of 64 rows of `pitch` elements
+    extern __shared__ __align__(16) __nv_bfloat16 pooled_rows[];   // kPooledMmaStages stages of 64 rows of `pitch` elements
     const int row_width = L.dk + L.dv, pitch = row_width + 8;      // rows 16 bytes apart modulo 128: no bank is met twice
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int first_row = tiles[2 * blockIdx.x], count = tiles[2 * blockIdx.x + 1];
@@ -372,8 +372,12 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
         return page;
     };
     int page_ahead = lookup(tile_begin);
-    auto load = [&](int stage, int tile) {
-        __nv_bfloat16* destination = pooled_rows + (static_cast<size_t>(stage) * kPooledMmaKeys + load_row) * pitch;
+    auto load = [&](int tile) {   // a tile past the CTA's last is an empty group: every turn commits one, so that one wait fits all
+        if (tile >= tile_end) {
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+            return;
+        }
+        __nv_bfloat16* destination = pooled_rows + (static_cast<size_t>(tile % kPooledMmaStages) * kPooledMmaKeys + load_row) * pitch;
         const bool pooled = tile < pooled_tiles;
         const int where = (pooled ? tile * kPooledMmaKeys : (first_token_tile + tile - pooled_tiles) * kPooledMmaKeys) + load_row;
         const int page = page_ahead;
@@ -383,7 +387,8 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
         asm volatile("cp.async.commit_group;\n" ::: "memory");
         page_ahead = lookup(tile + 1);
     };
-    if (tile_begin < tile_end) load(tile_begin & 1, tile_begin);
+#pragma unroll
+    for (int ahead = 0; ahead < kPooledMmaStages - 1; ++ahead) load(tile_begin + ahead);
 
     // the warp's queries as A fragments, its rows' positions and what each of them sees
     const int row_g = token_block * 16 + g, row_g8 = row_g + 8;
@@ -409,13 +414,9 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
 
     for (int tile = tile_begin; tile < tile_end; ++tile) {
-        const int stage = tile & 1;
-        if (tile + 1 < tile_end) {
-            load(stage ^ 1, tile + 1);   // that stage was used up in the turn before (the barrier at its end)
-            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-        }
+        const int stage = tile % kPooledMmaStages;
+        load(tile + kPooledMmaStages - 1);   // into the stage that was used up in the turn before (the barrier at its end)
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(kPooledMmaStages - 1) : "memory");
         __syncthreads();
         const bool pooled = tile < pooled_tiles;
         const int base = pooled ? tile * kPooledMmaKeys : (first_token_tile + tile - pooled_tiles) * kPooledMmaKeys;
@@ -532,10 +533,219 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     }
 }
 
+// ---------------------------------------------------------------- single tokens (decoding) on the tensor cores
+// A token that attends alone has one query a head, so the products are turned round: the rows of a product are 16 rows of the
+// cache, its columns up to 16 query heads of one K/V head.  S^T = K Q^T (A: the rows' keys straight from shared memory, B: the
+// queries from registers), the weights where the accumulators lie (four an element of a thread, not 32 as in a tile of tokens
+// of which one row is real), P^T rounded and moved into the B operand's layout by `movmatrix`, O^T += V^T P^T with V^T through
+// ldmatrix.trans.  Warps 0 to 3 take 16 of a block's 64 rows each (all eight warps copy); at the end their sums are added in warp
+// order through shared memory, turned back and rounded (or left in 32-bit for `pooled_finish` where CTAs share a token's rows).
+constexpr int kPooledSingleHeads = 16;   // query heads of one K/V head a CTA takes at most
+
+__device__ __forceinline__ uint32_t pooled_movmatrix_trans(uint32_t value) {
+    uint32_t result;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(result) : "r"(value));
+    return result;
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(32 * kPooledMmaWarps)
+pooled_attention_single_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages, const __nv_bfloat16* __restrict__ pooled_pages,
+                               __nv_bfloat16* __restrict__ out, const int* __restrict__ singles, const int* __restrict__ positions,
+                               const int* __restrict__ token_segment, const int* __restrict__ block_table, const int* __restrict__ pool_table,
+                               PooledLayout L, int heads, float scale, float cap, const float* __restrict__ head_bias, int window, int pool,
+                               const float* __restrict__ v_freq, int v_interleaved, int* status, float* __restrict__ partial, int total_rows) {
+    extern __shared__ __align__(16) __nv_bfloat16 pooled_rows[];   // kPooledMmaStages stages of 64 rows of `pitch` elements; at the end the warps' sums
+    const int row_width = L.dk + L.dv, pitch = row_width + 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int row = singles[blockIdx.x];
+    const int per_group = heads / L.groups, head_parts = (per_group + kPooledSingleHeads - 1) / kPooledSingleHeads;
+    const int group = blockIdx.y / head_parts, first_head = group * per_group + (blockIdx.y % head_parts) * kPooledSingleHeads;
+    const int num_heads = min(kPooledSingleHeads, group * per_group + per_group - first_head);
+    const int segment = token_segment[row];
+    const int p_last = positions[row];
+    const int blocks_seen = pool > 0 ? max(0, p_last - window + 1) / pool : 0;
+    const int first_key = max(0, p_last - window + 1);
+    const int pooled_tiles = (blocks_seen + kPooledMmaKeys - 1) / kPooledMmaKeys;
+    const int first_token_tile = first_key / kPooledMmaKeys, token_tiles = p_last / kPooledMmaKeys - first_token_tile + 1;
+    const int all_tiles = pooled_tiles + token_tiles;
+    const int tile_begin = static_cast<int>(static_cast<long long>(all_tiles) * blockIdx.z / gridDim.z);
+    const int tile_end = static_cast<int>(static_cast<long long>(all_tiles) * (blockIdx.z + 1) / gridDim.z);
+    const int chunks = row_width / 8;
+    const size_t group_offset = static_cast<size_t>(group) * row_width, row_stride = static_cast<size_t>(L.groups) * row_width;
+
+    const int load_row = threadIdx.x >> 2, load_part = threadIdx.x & 3;
+    auto lookup = [&](int tile) -> int {
+        if (tile >= tile_end) return -1;
+        const bool pooled = tile < pooled_tiles;
+        const int where = (pooled ? tile * kPooledMmaKeys : (first_token_tile + tile - pooled_tiles) * kPooledMmaKeys) + load_row;
+        if (!(pooled ? where < blocks_seen : (where >= first_key && where <= p_last))) return -1;
+        const int page = pooled ? pooled_page(pool_table, L, segment, where) : token_page(block_table, L, segment, where);
+        if (page < 0) report_error(status, kBadPage);
+        return page;
+    };
+    int page_ahead = lookup(tile_begin);
+    auto load = [&](int tile) {
+        if (tile >= tile_end) {
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+            return;
+        }
+        __nv_bfloat16* destination = pooled_rows + (static_cast<size_t>(tile % kPooledMmaStages) * kPooledMmaKeys + load_row) * pitch;
+        const bool pooled = tile < pooled_tiles;
+        const int where = (pooled ? tile * kPooledMmaKeys : (first_token_tile + tile - pooled_tiles) * kPooledMmaKeys) + load_row;
+        const int page = page_ahead;
+        const int per_page = pooled ? L.pool_rows : L.page_size;
+        const __nv_bfloat16* source = (pooled ? pooled_pages : pages) + (page < 0 ? 0 : (static_cast<size_t>(page) * per_page + where % per_page) * row_stride + group_offset);
+        for (int chunk = load_part; chunk < chunks; chunk += 4) pooled_copy_16(destination + 8 * chunk, source + 8 * chunk, page >= 0);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        page_ahead = lookup(tile + 1);
+    };
+#pragma unroll
+    for (int ahead = 0; ahead < kPooledMmaStages - 1; ++ahead) load(tile_begin + ahead);
+
+    // the queries as B operands: head tile n, column g is head first_head + 8 n + g
+    constexpr int kHeadTiles = kPooledSingleHeads / 8;
+    uint32_t q_b[DK / 16][kHeadTiles][2];
+#pragma unroll
+    for (int n = 0; n < kHeadTiles; ++n) {
+        const bool real = 8 * n + g < num_heads;
+        const __nv_bfloat16* q_head = q + (static_cast<size_t>(row) * heads + first_head + (real ? 8 * n + g : 0)) * L.dk;
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+            const bool in_k = real && 16 * ks < L.dk;
+            q_b[ks][n][0] = in_k ? *reinterpret_cast<const uint32_t*>(q_head + 16 * ks + 2 * t) : 0u;
+            q_b[ks][n][1] = in_k ? *reinterpret_cast<const uint32_t*>(q_head + 16 * ks + 8 + 2 * t) : 0u;
+        }
+    }
+    // an accumulator's columns are heads 8 n + 2 t and 8 n + 2 t + 1: their biases
+    float offsets[kHeadTiles][2];
+    const PooledWeight weight_of(scale, cap, 0.0f);
+#pragma unroll
+    for (int n = 0; n < kHeadTiles; ++n)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int head = 8 * n + 2 * t + e;
+            const float bias = head_bias != nullptr && head < num_heads ? head_bias[first_head + head] : 0.0f;
+            offsets[n][e] = PooledWeight(scale, cap, bias).offset;
+        }
+    float o[DV / 16][kHeadTiles][4];   // rows: channels 16 m + g (+8); columns: heads 8 n + 2 t (+1)
+#pragma unroll
+    for (int m = 0; m < DV / 16; ++m)
+#pragma unroll
+        for (int n = 0; n < kHeadTiles; ++n) o[m][n][0] = o[m][n][1] = o[m][n][2] = o[m][n][3] = 0.0f;
+    const bool second_tile = num_heads > 8;
+
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+        const int stage = tile % kPooledMmaStages;
+        load(tile + kPooledMmaStages - 1);
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(kPooledMmaStages - 1) : "memory");
+        __syncthreads();
+        const bool pooled = tile < pooled_tiles;
+        const int base = (pooled ? tile * kPooledMmaKeys : (first_token_tile + tile - pooled_tiles) * kPooledMmaKeys) + 16 * warp;   // the warp's 16 rows
+        const bool any = warp < kPooledMmaKeys / 16 && (pooled ? base < blocks_seen : (base <= p_last && base + 15 >= first_key));
+        if (any) {
+            const __nv_bfloat16* rows = pooled_rows + (static_cast<size_t>(stage) * kPooledMmaKeys + 16 * warp) * pitch;
+            float sc[kHeadTiles][4];
+#pragma unroll
+            for (int n = 0; n < kHeadTiles; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < DK / 16; ++ks) {
+                if (16 * ks < L.dk) {
+                    uint32_t k_a[4];
+                    const __nv_bfloat16* k_row = rows + static_cast<size_t>(g) * pitch + 16 * ks + 2 * t;
+                    k_a[0] = *reinterpret_cast<const uint32_t*>(k_row);
+                    k_a[1] = *reinterpret_cast<const uint32_t*>(k_row + 8 * pitch);
+                    k_a[2] = *reinterpret_cast<const uint32_t*>(k_row + 8);
+                    k_a[3] = *reinterpret_cast<const uint32_t*>(k_row + 8 * pitch + 8);
+                    pooled_mma(sc[0], k_a, q_b[ks][0][0], q_b[ks][0][1]);
+                    if (second_tile) pooled_mma(sc[1], k_a, q_b[ks][1][0], q_b[ks][1][1]);
+                }
+            }
+            // sc[n][0..1]: row g of the warp's 16; sc[n][2..3]: row g + 8
+            const int where_low = base + g, where_high = base + g + 8;
+            const bool seen_low = pooled ? where_low < blocks_seen : (where_low >= first_key && where_low <= p_last);
+            const bool seen_high = pooled ? where_high < blocks_seen : (where_high >= first_key && where_high <= p_last);
+            uint32_t p_b[kHeadTiles][2];
+#pragma unroll
+            for (int n = 0; n < kHeadTiles; ++n) {
+                float w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float x = weight_of.capped ? pooled_reciprocal(1.0f + pooled_exp2(sc[n][e] * weight_of.to_exponent)) : sc[n][e];
+                    const float value = pooled_reciprocal(1.0f + pooled_exp2(fmaf(x, weight_of.slope, offsets[n][e & 1])));
+                    w[e] = (e < 2 ? seen_low : seen_high) ? value : 0.0f;
+                }
+                // (row g, heads 2 t, 2 t + 1) -> (head g, rows 2 t, 2 t + 1): the B operand of the second product
+                p_b[n][0] = pooled_movmatrix_trans(pooled_pack(w[0], w[1]));
+                p_b[n][1] = pooled_movmatrix_trans(pooled_pack(w[2], w[3]));
+            }
+            // V^T as A operand: four 8 x 8 pieces, rows 0-7 / 8-15 of the warp's 16 x channels 16 m (+8); lane l gives row l % 8 of piece l / 8
+            const __nv_bfloat16* v_rows = rows + static_cast<size_t>((lane & 7) + (lane >> 4) * 8) * pitch + L.dk + ((lane >> 3) & 1) * 8;
+#pragma unroll
+            for (int m = 0; m < DV / 16; ++m) {
+                if (16 * m < L.dv) {
+                    uint32_t v_a[4];
+                    pooled_ldmatrix_x4_trans(v_a, v_rows + 16 * m);
+                    pooled_mma(o[m][0], v_a, p_b[0][0], p_b[0][1]);
+                    if (second_tile) pooled_mma(o[m][1], v_a, p_b[1][0], p_b[1][1]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // the four warps' sums side by side in shared memory: [warp][channel][head]
+    float* sums = reinterpret_cast<float*>(pooled_rows);
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+    if (warp < kPooledMmaKeys / 16) {
+#pragma unroll
+        for (int m = 0; m < DV / 16; ++m) {
+            if (16 * m >= L.dv) continue;
+#pragma unroll
+            for (int n = 0; n < kHeadTiles; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int channel = 16 * m + g + (e >= 2 ? 8 : 0), head = 8 * n + 2 * t + (e & 1);
+                    sums[(static_cast<size_t>(warp) * L.dv + channel) * kPooledSingleHeads + head] = o[m][n][e];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const int half = L.dv / 2;
+    for (int index = threadIdx.x; index < num_heads * half; index += blockDim.x) {
+        const int head = index / half, pair = index - head * half;
+        const int first = v_interleaved ? 2 * pair : pair, second = v_interleaved ? 2 * pair + 1 : pair + half;
+        float a = 0.0f, b = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kPooledMmaKeys / 16; ++w) {
+            a += sums[(static_cast<size_t>(w) * L.dv + first) * kPooledSingleHeads + head];
+            b += sums[(static_cast<size_t>(w) * L.dv + second) * kPooledSingleHeads + head];
+        }
+        const size_t offset = (static_cast<size_t>(row) * heads + first_head + head) * L.dv;
+        if (partial != nullptr) {
+            float* destination = partial + static_cast<size_t>(blockIdx.z) * total_rows * heads * L.dv + offset;
+            destination[first] = a;
+            destination[second] = b;
+            continue;
+        }
+        if (v_freq != nullptr) {
+            float sine, cosine;
+            sincosf(static_cast<float>(p_last) * v_freq[pair], &sine, &cosine);
+            const float turned = a * cosine + b * sine;
+            b = b * cosine - a * sine;
+            a = turned;
+        }
+        out[offset + first] = __float2bfloat16_rn(a);
+        out[offset + second] = __float2bfloat16_rn(b);
+    }
+}
+
 // grid (rows), a thread per head and pair of channels: out = the shares' sums added in order, turned back by the row's position.
+// `rows` (may be null): the rows to finish, one a block.
 __global__ void pooled_finish_kernel(const float* __restrict__ partial, int shares, __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
-                                     int total_rows, int heads, int dv, const float* __restrict__ v_freq, int v_interleaved) {
-    const int row = blockIdx.x;
+                                     int total_rows, int heads, int dv, const float* __restrict__ v_freq, int v_interleaved, const int* __restrict__ rows) {
+    const int row = rows != nullptr ? rows[blockIdx.x] : static_cast<int>(blockIdx.x);
     const float p = static_cast<float>(positions[row]);
     const size_t share_stride = static_cast<size_t>(total_rows) * heads * dv;
     for (int index = threadIdx.x; index < heads * (dv / 2); index += blockDim.x) {
@@ -623,26 +833,64 @@ int lb_pooled_attention_mma(const void* q, const void* pages, const void* pooled
     lb::PooledLayout L{page_size, num_pages, max_blocks, pool_rows > 0 ? pool_rows : 1, pool_pages, pool_max_blocks, groups, dk, dv};
     const int per_group = heads / groups;
     const dim3 grid(num_tiles, groups * ((per_group + head_block - 1) / head_block), shares);
-    const size_t shared = 2 * static_cast<size_t>(lb::kPooledMmaKeys) * (dk + dv + 8) * sizeof(__nv_bfloat16);
+    const size_t shared = static_cast<size_t>(lb::kPooledMmaStages) * lb::kPooledMmaKeys * (dk + dv + 8) * sizeof(__nv_bfloat16);
     const auto* q16 = static_cast<const __nv_bfloat16*>(q);
     const auto* pages16 = static_cast<const __nv_bfloat16*>(pages);
     const auto* pooled16 = static_cast<const __nv_bfloat16*>(pooled_pages);
     auto* out16 = static_cast<__nv_bfloat16*>(out);
     if (dk <= 64 && dv <= 64) {
         static lb::OncePerDevice once;
-        lb::allow_shared_memory(once, lb::pooled_attention_mma_kernel<64, 64>, 2 * lb::kPooledMmaKeys * (128 + 8) * 2);
+        lb::allow_shared_memory(once, lb::pooled_attention_mma_kernel<64, 64>, lb::kPooledMmaStages * lb::kPooledMmaKeys * (128 + 8) * 2);
         lb::pooled_attention_mma_kernel<64, 64><<<grid, 32 * lb::kPooledMmaWarps, shared, stream>>>(
             q16, pages16, pooled16, out16, tiles, positions, token_segment, block_table, pool_table, L, heads, head_block, scale, cap, head_bias, window, pool, v_freq,
             v_interleaved, status, partial, total_rows);
     } else {
         static lb::OncePerDevice once;
-        lb::allow_shared_memory(once, lb::pooled_attention_mma_kernel<128, 128>, 2 * lb::kPooledMmaKeys * (256 + 8) * 2);
+        lb::allow_shared_memory(once, lb::pooled_attention_mma_kernel<128, 128>, lb::kPooledMmaStages * lb::kPooledMmaKeys * (256 + 8) * 2);
         lb::pooled_attention_mma_kernel<128, 128><<<grid, 32 * lb::kPooledMmaWarps, shared, stream>>>(
             q16, pages16, pooled16, out16, tiles, positions, token_segment, block_table, pool_table, L, heads, head_block, scale, cap, head_bias, window, pool, v_freq,
             v_interleaved, status, partial, total_rows);
     }
     if (shares > 1)
-        lb::pooled_finish_kernel<<<total_rows, 256, 0, stream>>>(partial, shares, out16, positions, total_rows, heads, dv, v_freq, v_interleaved);
+        lb::pooled_finish_kernel<<<total_rows, 256, 0, stream>>>(partial, shares, out16, positions, total_rows, heads, dv, v_freq, v_interleaved, nullptr);
+    return LB_LAUNCH_RESULT();
+}
+
+// Tokens that attend alone: `singles` lists their rows.  shares > 1: that many CTAs share out a token's rows of the cache; `partial`
+// then holds shares x total_rows x heads x dv floats (only the listed rows are written and read).
+int lb_pooled_attention_single(const void* q, const void* pages, const void* pooled_pages, void* out, const int* singles, int num_singles, const int* positions,
+                               const int* token_segment, const int* block_table, const int* pool_table, int heads, int groups, int dk, int dv, int page_size,
+                               int num_pages, int max_blocks, int pool_rows, int pool_pages, int pool_max_blocks, float scale, float cap,
+                               const float* head_bias, int window, int pool, const float* v_freq, int v_interleaved, int* status, cudaStream_t stream, int shares,
+                               float* partial, int total_rows) {
+    if (num_singles == 0) return 0;
+    if (heads % groups != 0 || dk % 16 != 0 || dv % 16 != 0 || dk < 16 || dv < 16 || dk > 128 || dv > 128 || window < 1 || pool < 0) return -2;
+    if (shares < 1 || shares > 64 || (shares > 1 && partial == nullptr)) return -2;
+    if (shares == 1) partial = nullptr;
+    lb::PooledLayout L{page_size, num_pages, max_blocks, pool_rows > 0 ? pool_rows : 1, pool_pages, pool_max_blocks, groups, dk, dv};
+    const int per_group = heads / groups;
+    const dim3 grid(num_singles, groups * ((per_group + lb::kPooledSingleHeads - 1) / lb::kPooledSingleHeads), shares);
+    // the stages, and at the end four warps' sums of dv x 16 floats (no more than the stages)
+    const size_t shared = static_cast<size_t>(lb::kPooledMmaStages) * lb::kPooledMmaKeys * (dk + dv + 8) * sizeof(__nv_bfloat16);
+    const auto* q16 = static_cast<const __nv_bfloat16*>(q);
+    const auto* pages16 = static_cast<const __nv_bfloat16*>(pages);
+    const auto* pooled16 = static_cast<const __nv_bfloat16*>(pooled_pages);
+    auto* out16 = static_cast<__nv_bfloat16*>(out);
+    if (dk <= 64 && dv <= 64) {
+        static lb::OncePerDevice once;
+        lb::allow_shared_memory(once, lb::pooled_attention_single_kernel<64, 64>, lb::kPooledMmaStages * lb::kPooledMmaKeys * (128 + 8) * 2);
+        lb::pooled_attention_single_kernel<64, 64><<<grid, 32 * lb::kPooledMmaWarps, shared, stream>>>(
+            q16, pages16, pooled16, out16, singles, positions, token_segment, block_table, pool_table, L, heads, scale, cap, head_bias, window, pool, v_freq,
+            v_interleaved, status, partial, total_rows);
+    } else {
+        static lb::OncePerDevice once;
+        lb::allow_shared_memory(once, lb::pooled_attention_single_kernel<128, 128>, lb::kPooledMmaStages * lb::kPooledMmaKeys * (256 + 8) * 2);
+        lb::pooled_attention_single_kernel<128, 128><<<grid, 32 * lb::kPooledMmaWarps, shared, stream>>>(
+            q16, pages16, pooled16, out16, singles, positions, token_segment, block_table, pool_table, L, heads, scale, cap, head_bias, window, pool, v_freq,
+            v_interleaved, status, partial, total_rows);
+    }
+    if (shares > 1)
+        lb::pooled_finish_kernel<<<num_singles, 256, 0, stream>>>(partial, shares, out16, positions, total_rows, heads, dv, v_freq, v_interleaved, singles);
     return LB_LAUNCH_RESULT();
 }
 

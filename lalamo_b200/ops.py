@@ -1497,6 +1497,16 @@ def pooled_attention_shares(num_tiles: int, num_heads: int, num_groups: int, sms
     return 1 if ctas >= 4 * sms else max(1, min(16, -(-4 * sms // ctas)))
 
 
+POOLED_SINGLE_HEADS = 16  # query heads of one K/V head that a CTA of the single-token kernel takes at most
+
+
+def pooled_single_shares(num_singles: int, num_heads: int, num_groups: int, sms: int | None = None) -> int:
+    """As :func:`pooled_attention_shares`, for the kernel of tokens that attend alone."""
+    ctas = num_singles * num_groups * -(-(num_heads // num_groups) // POOLED_SINGLE_HEADS)
+    sms = sms or sm_count()
+    return 1 if ctas >= 4 * sms else max(1, min(16, -(-4 * sms // ctas)))
+
+
 def pooled_attention_supported(dtype: torch.dtype, head_dim: int, value_dim: int) -> bool:
     """Whether the tensor-core kernel takes these sizes (bfloat16, heads of multiples of 16 up to 128 channels)."""
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= head_dim <= 128 and 16 <= value_dim <= 128
@@ -1576,6 +1586,35 @@ def pooled_attention(q: torch.Tensor, pages: torch.Tensor, pool_pages: torch.Ten
                                           c_int(pool_blocks), c_int(head_block), c_float(scale), c_float(softcap), _ptr(head_bias), c_int(window), c_int(pool),
                                           _ptr(value_freq), c_int(1 if interleaved else 0), _ptr(status), _stream(), c_int(shares), _ptr(partial), c_int(tokens))
     _done(code, "pooled_attention", 2 if shares > 1 else 1)
+
+
+def pooled_attention_single(q: torch.Tensor, pages: torch.Tensor, pool_pages: torch.Tensor | None, out: torch.Tensor, *, singles: torch.Tensor, num_singles: int,
+                            shares: int | None = None, positions: torch.Tensor, token_segment: torch.Tensor, block_table: torch.Tensor,
+                            pool_table: torch.Tensor | None, num_heads: int, num_groups: int, head_dim: int, value_dim: int, scale: float, softcap: float,
+                            head_bias: torch.Tensor | None, window: int, pool: int, value_freq: torch.Tensor | None, interleaved: bool = False,
+                            status: torch.Tensor) -> None:
+    """The same attention for tokens that attend alone (``singles``: their rows, int32), on the tensor cores with the products turned
+    round: 16 rows of the cache are a product's rows, up to 16 query heads of a K/V head its columns.  Same sizes, arithmetic and
+    order of the rows as :func:`pooled_attention`; other rows of ``out`` are left alone."""
+    tokens, (count, page_size, max_blocks), (pool_count, pool_rows, pool_blocks) = _pooled_arguments(
+        q, pages, pool_pages, out, positions, token_segment, block_table, pool_table, num_heads, num_groups, head_dim, value_dim, head_bias, window, pool,
+        value_freq, "pooled_attention_single")
+    if not pooled_attention_supported(q.dtype, head_dim, value_dim):
+        raise KernelError("pooled_attention_single: the tensor-core kernel takes bfloat16 and heads of multiples of 16 up to 128 channels")
+    _check(singles, "singles", torch.int32)
+    if singles.numel() < num_singles:
+        raise KernelError("pooled_attention_single: fewer rows listed than announced")
+    if shares is None:
+        shares = pooled_single_shares(num_singles, num_heads, num_groups)
+    if not 1 <= shares <= 64:
+        raise KernelError("pooled_attention_single: 1 to 64 shares")
+    partial = torch.empty(shares, tokens, num_heads * value_dim, dtype=torch.float32, device=q.device) if shares > 1 else None
+    code = _lib().lb_pooled_attention_single(_ptr(q), _ptr(pages), _ptr(pool_pages if pool else None), _ptr(out), _ptr(singles), c_int(num_singles), _ptr(positions),
+                                             _ptr(token_segment), _ptr(block_table), _ptr(pool_table if pool else None), c_int(num_heads), c_int(num_groups),
+                                             c_int(head_dim), c_int(value_dim), c_int(page_size), c_int(count), c_int(max_blocks), c_int(pool_rows), c_int(pool_count),
+                                             c_int(pool_blocks), c_float(scale), c_float(softcap), _ptr(head_bias), c_int(window), c_int(pool),
+                                             _ptr(value_freq), c_int(1 if interleaved else 0), _ptr(status), _stream(), c_int(shares), _ptr(partial), c_int(tokens))
+    _done(code, "pooled_attention_single", 2 if shares > 1 else 1)
 
 
 # ------------------------------------------------------------------------------ sampling

@@ -6,8 +6,9 @@ retention rule (pages go back once the window and every unfinished block have pa
 row per block, which are kept for good.  A step rotates q, k and v and writes the pages, computes the mean of every block it completed from the pages, and
 then attends: the visible blocks first, then the window's positions upwards, the weights ``sigmoid(cap(q . k scale) +
 bias_h)`` summed with the values in 32-bit without any normalisation; rotated values are turned back by the query's
-position at the end.  In bfloat16, for heads of multiples of 16 channels, the attention runs on the tensor cores in tiles of
-consecutive tokens (single decoded tokens are tiles of one); otherwise, and in 32-bit, a block per token and head computes it plainly."""
+position at the end.  In bfloat16, for heads of multiples of 16 channels, the attention runs on the tensor cores: portions in tiles of
+consecutive tokens, tokens that attend alone (decoding) on a kernel of their own whose products have the cache's rows as rows and the
+query heads as columns; otherwise, and in 32-bit, a block per token and head computes it plainly."""
 
 from __future__ import annotations
 
@@ -85,13 +86,15 @@ class PooledWindowAttention(Mixer):
     step_plan_uses_context = False
 
     def step_plan_key(self) -> object:
-        return ("pooled_window_attention", self.tile_tokens)
+        return ("pooled_window_attention", self.tile_tokens)   # tiles and single tokens
 
     def plan_step(self, segments: HostSegments) -> dict[str, np.ndarray]:
-        """``tiles``: ``(first row, count)`` of each run of at most ``tile_tokens`` consecutive tokens of a portion."""
-        tiles = [(first, min(self.tile_tokens, start + length - first)) for start, length in zip(segments.start, segments.length)
+        """``singles``: the rows of portions of one token (they attend alone); ``tiles``: ``(first row, count)`` of each run of at most
+        ``tile_tokens`` consecutive tokens of a longer portion."""
+        singles = [start for start, length in zip(segments.start, segments.length) if length == 1]
+        tiles = [(first, min(self.tile_tokens, start + length - first)) for start, length in zip(segments.start, segments.length) if length > 1
                  for first in range(start, start + length, self.tile_tokens)]
-        return {"tiles": np.asarray(tiles, dtype=np.int32).reshape(-1)}
+        return {"singles": np.asarray(singles, dtype=np.int32), "tiles": np.asarray(tiles, dtype=np.int32).reshape(-1)}
 
     can_accumulate = True
 
@@ -120,7 +123,10 @@ class PooledWindowAttention(Mixer):
         pool_pages = blocks_view.k_pages if blocks_view is not None else None
         if self.on_tensor_cores:
             lists, host_lists = step.plan_of(self)
-            ops.pooled_attention(queries, tokens_view.k_pages, pool_pages, mixed, tiles=lists["tiles"], num_tiles=host_lists["tiles"].size // 2, **common)
+            if host_lists["singles"].size:
+                ops.pooled_attention_single(queries, tokens_view.k_pages, pool_pages, mixed, singles=lists["singles"], num_singles=host_lists["singles"].size, **common)
+            if host_lists["tiles"].size:
+                ops.pooled_attention(queries, tokens_view.k_pages, pool_pages, mixed, tiles=lists["tiles"], num_tiles=host_lists["tiles"].size // 2, **common)
         else:
             ops.pooled_attention_plain(queries, tokens_view.k_pages, pool_pages, mixed, **common)
         if residual is not None:

@@ -239,11 +239,12 @@ def test_router_with_a_choice_bias_and_experts_without_a_gate():
     assert torch.allclose(stream.double().cpu(), want + scores[:, experts : experts + 1] * shared.double(), rtol=2e-2, atol=2e-2)
 
 
-def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size, contexts, lengths, cap, seed, tensor_cores=False, shares=None):
+def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size, contexts, lengths, cap, seed, tensor_cores=False, shares=None, alone=True):
     """One step of the pooled attention's kernels over requests that hold ``contexts`` tokens already and bring ``lengths`` more (the
     earlier tokens go through the same kernels, one request a step, in uneven portions), against the plain attention over each
     request's whole sequence.  Pages are handed out in a scattered order.  ``tensor_cores``: the last step's attention on the tensor-core
-    kernel, in tiles of consecutive tokens (``shares``: so many CTAs share out a tile's rows; left out, the launch's shape decides)."""
+    kernels: portions in tiles of consecutive tokens, portions of one token on the kernel of tokens that attend alone (``alone=False``: as
+    tiles of one token too); ``shares``: so many CTAs share out a tile's rows; left out, the launch's shape decides."""
     from lalamo_b200 import ops
 
     device = torch.device("cuda")
@@ -284,8 +285,13 @@ def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size,
         if on_tensor_cores:
             size = ops.pooled_attention_tiling(heads, groups)[1]
             starts = np.cumsum([0] + [count for _, _, count in portions[:-1]]).tolist()
-            tiles = [(first, min(size, start + count - first)) for start, (_, _, count) in zip(starts, portions) for first in range(start, start + count, size)]
-            ops.pooled_attention(q, token_pages, pool_pages, out, tiles=as_int([v for tile in tiles for v in tile]), num_tiles=len(tiles), shares=shares, **common)
+            tiles = [(first, min(size, start + count - first)) for start, (_, _, count) in zip(starts, portions) if count > 1 or not alone
+                     for first in range(start, start + count, size)]
+            singles = [start for start, (_, _, count) in zip(starts, portions) if count == 1 and alone]
+            if tiles:
+                ops.pooled_attention(q, token_pages, pool_pages, out, tiles=as_int([v for tile in tiles for v in tile]), num_tiles=len(tiles), shares=shares, **common)
+            if singles:
+                ops.pooled_attention_single(q, token_pages, pool_pages, out, singles=as_int(singles), num_singles=len(singles), shares=shares, **common)
         else:
             ops.pooled_attention_plain(q, token_pages, pool_pages, out, **common)
         return out
@@ -360,10 +366,12 @@ def test_pooled_attention_on_the_tensor_cores_at_every_edge():
         dict(heads=8, groups=8, dk=64, dv=48, window=96, pool=8, rot_dims=64, page_size=16, contexts=[0, 95, 103, 104, 200, 700], lengths=[130, 1, 1, 1, 17, 1], cap=30.0),
         dict(heads=4, groups=1, dk=128, dv=128, window=70, pool=5, rot_dims=64, page_size=16, contexts=[0, 69, 330], lengths=[150, 3, 1], cap=30.0),
         dict(heads=6, groups=3, dk=80, dv=96, window=130, pool=2, rot_dims=80, page_size=32, contexts=[0, 260], lengths=[200, 66], cap=12.0),
+        dict(heads=40, groups=2, dk=32, dv=48, window=33, pool=7, rot_dims=16, page_size=16, contexts=[0, 1, 32, 33, 39, 40, 41, 200], lengths=[1] * 8, cap=25.0),
+        dict(heads=9, groups=1, dk=48, dv=16, window=50, pool=6, rot_dims=48, page_size=16, contexts=[49, 55, 56, 120], lengths=[1, 1, 1, 1], cap=0.0),
     ]
     for index, case in enumerate(cases):
-        for shares in (1, None, 5):   # every tile's rows in one CTA, as the launch's shape decides, and shared out over five
-            assert pooled_case(torch.bfloat16, seed=40 + index, tensor_cores=True, shares=shares, **case) < 2e-2, (case, shares)
+        for shares, alone in ((1, True), (None, True), (5, True), (1, False), (5, False)):   # every tile's rows in one CTA, as the launch's shape decides, shared out over five
+            assert pooled_case(torch.bfloat16, seed=40 + index, tensor_cores=True, shares=shares, alone=alone, **case) < 2e-2, (case, shares, alone)
 
 
 # ----------------------------------------------------------------------------- whole models
