@@ -64,8 +64,8 @@ CONFIG_C = model(256, 128, [
     layer("parallel", {"left": left(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=32, base=1000.0, scale=0.125, softcap=30.0, size=64, pool=8),
                        "right": right(heads=2, dim=64, vdim=64, tau=16.0)}, moe(experts=8, top=2, ff=64, scale=2.0, shared_ff=64)),
     layer("retention", retention(heads=2, dim=64, vdim=128), moe(experts=8, top=2, ff=64, scale=2.0, shared_ff=64)),
-    layer("parallel", {"left": left(heads=4, kv_heads=4, dim=32, vdim=48, rot_dims=32, base=1e6, scale=0.2, softcap=30.0, size=96, pool=8),
-                       "right": right(heads=4, dim=32, vdim=32, tau=16.0)}, None),
+    layer("parallel", {"left": left(heads=4, kv_heads=4, dim=32, vdim=64, rot_dims=32, base=5e5, scale=0.2, softcap=25.0, size=80, pool=10),
+                       "right": right(heads=2, dim=32, vdim=64, tau=12.0)}, None),
 ])
 
 # D, E, F, G: one layer each without a feed-forward (the mixers alone), and a feed-forward behind the smallest mixer.
