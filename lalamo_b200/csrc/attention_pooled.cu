@@ -20,6 +20,8 @@
 // block b in page pool_table[b / pool_rows], row b % pool_rows.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace lb {
 
 struct PooledLayout {
@@ -262,7 +264,7 @@ pooled_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pag
 // (HB * TB = 8, HB at most 4: a warp is one head's 16 tokens).  Rows of the cache come 64 at a time through four cp.async stages, first the
 // pooled blocks from block 0 on, then the positions from the multiple of 64 at or below the tile's first visible one: so the
 // tiles a query's keys fall into, and with them the order of its sums, depend on its position alone.  Rows that no query
-// of the CTA sees are zero-filled and never read.  S = Q K^T (m16n8k16, K straight from the rows), the weights in 32-bit with
+// of the CTA sees are zero-filled and never read.  S = Q K^T (m16n8k16, K through ldmatrix from the rows), the weights in 32-bit with
 // a mask per element, P rounded to bfloat16 as the next product's A operand, O += P V with V through ldmatrix.trans from the
 // same rows.  At the end a head's sums are turned back by the query's position in registers (both channels of a pair lie in
 // one thread) and rounded once.  Where a launch has few CTAs (single decoded tokens), grid.z CTAs share out a tile's blocks of 64
@@ -278,6 +280,11 @@ __device__ __forceinline__ void pooled_mma(float (&c)[4], const uint32_t (&a)[4]
 __device__ __forceinline__ void pooled_ldmatrix_x4_trans(uint32_t (&r)[4], const void* shared_address) {
     const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(shared_address));
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+
+__device__ __forceinline__ void pooled_ldmatrix_x4(uint32_t (&r)[4], const void* shared_address) {
+    const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(shared_address));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
 }
 
 // 16 bytes from global to shared memory, or 16 zero bytes (nothing is read) if `valid` is false.
@@ -319,6 +326,12 @@ struct PooledWeight {
     }
     __device__ __forceinline__ float operator()(float dot) const {
         const float x = capped ? pooled_reciprocal(1.0f + pooled_exp2(dot * to_exponent)) : dot;
+        return pooled_reciprocal(1.0f + pooled_exp2(fmaf(x, slope, offset)));
+    }
+    // the same with the branch decided at compile time, for loops whose elements should interleave
+    template <bool CAPPED>
+    __device__ __forceinline__ float value(float dot) const {
+        const float x = CAPPED ? pooled_reciprocal(1.0f + pooled_exp2(dot * to_exponent)) : dot;
         return pooled_reciprocal(1.0f + pooled_exp2(fmaf(x, slope, offset)));
     }
 };
@@ -428,13 +441,17 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
             float sc[kPooledMmaKeys / 8][4];
 #pragma unroll
             for (int n = 0; n < kPooledMmaKeys / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+            // K as B operand, four 8 x 8 pieces at a time: rows 8 n (+8) x channels 16 ks (+8); lane l gives the address of row l % 8 of piece l / 8
+            const __nv_bfloat16* k_rows = rows + static_cast<size_t>((lane & 7) + (lane >> 4) * 8) * pitch + ((lane >> 3) & 1) * 8;
 #pragma unroll
             for (int ks = 0; ks < DK / 16; ++ks) {
                 if (16 * ks < L.dk) {
 #pragma unroll
-                    for (int n = 0; n < kPooledMmaKeys / 8; ++n) {
-                        const __nv_bfloat16* k_row = rows + static_cast<size_t>(8 * n + g) * pitch + 16 * ks + 2 * t;
-                        pooled_mma(sc[n], q_a[ks], *reinterpret_cast<const uint32_t*>(k_row), *reinterpret_cast<const uint32_t*>(k_row + 8));
+                    for (int n = 0; n < kPooledMmaKeys / 8; n += 2) {
+                        uint32_t k_b[4];
+                        pooled_ldmatrix_x4(k_b, k_rows + static_cast<size_t>(8 * n) * pitch + 16 * ks);
+                        pooled_mma(sc[n], q_a[ks], k_b[0], k_b[1]);
+                        pooled_mma(sc[n + 1], q_a[ks], k_b[2], k_b[3]);
                     }
                 }
             }
@@ -442,25 +459,29 @@ pooled_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
             const bool all_seen = token_block * 16 + 15 < count &&
                                   (pooled ? base + kPooledMmaKeys <= (pool > 0 ? max(0, p_low - window + 1) / pool : 0)
                                           : (base + kPooledMmaKeys - 1 <= p_low && base + window > p_low + 15));
-            if (all_seen) {
+            auto weigh = [&](auto capped_tag) {
+                constexpr bool kCapped = decltype(capped_tag)::value;
+                if (all_seen) {
 #pragma unroll
-                for (int n = 0; n < kPooledMmaKeys / 8; ++n) {
+                    for (int n = 0; n < kPooledMmaKeys / 8; ++n) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) sc[n][e] = weight_of(sc[n][e]);
-                }
-            } else {
+                        for (int e = 0; e < 4; ++e) sc[n][e] = weight_of.template value<kCapped>(sc[n][e]);
+                    }
+                } else {
 #pragma unroll
-                for (int n = 0; n < kPooledMmaKeys / 8; ++n) {
+                    for (int n = 0; n < kPooledMmaKeys / 8; ++n) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int where = base + 8 * n + 2 * t + (e & 1);
-                        const bool upper = e < 2;   // row g; else row g + 8
-                        const bool seen = pooled ? where < (upper ? seen_g : seen_g8)
-                                                 : (upper ? (live_g && where <= p_g && where + window > p_g) : (live_g8 && where <= p_g8 && where + window > p_g8));
-                        sc[n][e] = seen ? weight_of(sc[n][e]) : 0.0f;
+                        for (int e = 0; e < 4; ++e) {
+                            const int where = base + 8 * n + 2 * t + (e & 1);
+                            const bool upper = e < 2;   // row g; else row g + 8
+                            const bool seen = pooled ? where < (upper ? seen_g : seen_g8)
+                                                     : (upper ? (live_g && where <= p_g && where + window > p_g) : (live_g8 && where <= p_g8 && where + window > p_g8));
+                            sc[n][e] = seen ? weight_of.template value<kCapped>(sc[n][e]) : 0.0f;
+                        }
                     }
                 }
-            }
+            };
+            if (weight_of.capped) weigh(std::true_type{}); else weigh(std::false_type{});
 #pragma unroll
             for (int kk = 0; kk < kPooledMmaKeys / 16; ++kk) {
                 uint32_t p_a[4];

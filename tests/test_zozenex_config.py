@@ -167,3 +167,17 @@ def test_the_plain_mechanisms_on_hand_made_cases():
     out = plain.routed_experts(torch.ones(1, 1, dtype=torch.float64), w, cfg)
     # choice scores: 0.88 - 1, 0.5, 0.12 + 0.9 -> the third expert, weighed by sigmoid(-2) * 2
     assert torch.allclose(out, torch.sigmoid(torch.tensor(-2.0, dtype=torch.float64)) * 2.0 * 3.0 * plain.gelu(torch.ones(1, 1, dtype=torch.float64)))
+
+
+def test_how_the_tensor_core_attention_divides_a_step():
+    """A CTA's eight warps are one query head's 16 tokens each: the fewer heads a K/V head has, the longer the tiles; launches of few CTAs
+    share out a tile's rows, by the launch's shape alone."""
+    from lalamo_b200 import ops
+
+    assert [ops.pooled_attention_tiling(heads, groups) for heads, groups in ((8, 8), (8, 4), (6, 2), (16, 4), (40, 2))] == [(1, 128), (2, 64), (3, 32), (4, 32), (4, 32)]
+    assert ops.pooled_attention_supported(torch.bfloat16, 64, 48) and ops.pooled_attention_supported(torch.bfloat16, 128, 16)
+    assert not ops.pooled_attention_supported(torch.float32, 64, 64) and not ops.pooled_attention_supported(torch.bfloat16, 24, 64)
+    assert not ops.pooled_attention_supported(torch.bfloat16, 64, 144)
+    for shares_of in (lambda n: ops.pooled_attention_shares(n, 16, 4, sms=148), lambda n: ops.pooled_single_shares(n, 16, 4, sms=148)):
+        counts = [shares_of(n) for n in (1, 8, 64, 148, 1000)]
+        assert counts[0] == 16 and counts[-1] == 1 and all(a >= b for a, b in zip(counts, counts[1:])) and all(1 <= c <= 16 for c in counts)
