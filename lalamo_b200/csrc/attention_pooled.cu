@@ -763,10 +763,13 @@ pooled_attention_single_kernel(const __nv_bfloat16* __restrict__ q, const __nv_b
 }
 
 // grid (rows), a thread per head and pair of channels: out = the shares' sums added in order, turned back by the row's position.
-// `rows` (may be null): the rows to finish, one a block.
+// Only the rows the attention kernel before it wrote are finished: `rows` lists them, one a block (tokens that attend alone), or `tiles`
+// does ((first row, count) a tile; grid (tiles, tokens a tile has at most)).
 __global__ void pooled_finish_kernel(const float* __restrict__ partial, int shares, __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
-                                     int total_rows, int heads, int dv, const float* __restrict__ v_freq, int v_interleaved, const int* __restrict__ rows) {
-    const int row = rows != nullptr ? rows[blockIdx.x] : static_cast<int>(blockIdx.x);
+                                     int total_rows, int heads, int dv, const float* __restrict__ v_freq, int v_interleaved, const int* __restrict__ rows,
+                                     const int* __restrict__ tiles) {
+    if (tiles != nullptr && static_cast<int>(blockIdx.y) >= tiles[2 * blockIdx.x + 1]) return;
+    const int row = tiles != nullptr ? tiles[2 * blockIdx.x] + static_cast<int>(blockIdx.y) : rows[blockIdx.x];
     const float p = static_cast<float>(positions[row]);
     const size_t share_stride = static_cast<size_t>(total_rows) * heads * dv;
     for (int index = threadIdx.x; index < heads * (dv / 2); index += blockDim.x) {
@@ -873,7 +876,8 @@ int lb_pooled_attention_mma(const void* q, const void* pages, const void* pooled
             v_interleaved, status, partial, total_rows);
     }
     if (shares > 1)
-        lb::pooled_finish_kernel<<<total_rows, 256, 0, stream>>>(partial, shares, out16, positions, total_rows, heads, dv, v_freq, v_interleaved, nullptr);
+        lb::pooled_finish_kernel<<<dim3(num_tiles, 16 * (lb::kPooledMmaWarps / head_block)), 256, 0, stream>>>(partial, shares, out16, positions, total_rows, heads, dv, v_freq,
+                                                                                                            v_interleaved, nullptr, tiles);
     return LB_LAUNCH_RESULT();
 }
 
@@ -911,7 +915,7 @@ int lb_pooled_attention_single(const void* q, const void* pages, const void* poo
             v_interleaved, status, partial, total_rows);
     }
     if (shares > 1)
-        lb::pooled_finish_kernel<<<num_singles, 256, 0, stream>>>(partial, shares, out16, positions, total_rows, heads, dv, v_freq, v_interleaved, singles);
+        lb::pooled_finish_kernel<<<num_singles, 256, 0, stream>>>(partial, shares, out16, positions, total_rows, heads, dv, v_freq, v_interleaved, singles, nullptr);
     return LB_LAUNCH_RESULT();
 }
 

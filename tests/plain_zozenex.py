@@ -91,7 +91,7 @@ def pooled_sigmoid_attention(h: torch.Tensor, w: dict, cfg: dict) -> torch.Tenso
     k = rotate_halves((h @ w["k"].T).reshape(tokens, groups, dk), positions, rot_dims, base)
     v = rotate_halves((h @ w["v"].T).reshape(tokens, groups, dv), positions, dv, base)
     out = torch.zeros(tokens, heads, dv, dtype=DT)
-    cap = cfg["softcap"]
+    cap = cfg.get("softcap") or 0.0
     for i in range(tokens):
         first = max(0, i - window + 1)
         blocks = max(0, (i - window + 1) // pool)   # block b is seen if (b + 1) * pool - 1 <= i - window
@@ -104,7 +104,8 @@ def pooled_sigmoid_attention(h: torch.Tensor, w: dict, cfg: dict) -> torch.Tenso
         for head in range(heads):
             g = head // (heads // groups)
             score = (keys_i[:, g] @ q[i, head]) * cfg["scale"]
-            score = cap * torch.tanh(score / cap)
+            if cap:   # no cap where the configuration gives none (or zero)
+                score = cap * torch.tanh(score / cap)
             weight = torch.sigmoid(score + w["pb"][head])
             out[i, head] = weight @ values_i[:, g]
     out = rotate_halves(out, positions, dv, base, sign=-1.0)

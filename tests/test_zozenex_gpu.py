@@ -288,8 +288,15 @@ def pooled_case(dtype, heads, groups, dk, dv, window, pool, rot_dims, page_size,
             tiles = [(first, min(size, start + count - first)) for start, (_, _, count) in zip(starts, portions) if count > 1 or not alone
                      for first in range(start, start + count, size)]
             singles = [start for start, (_, _, count) in zip(starts, portions) if count == 1 and alone]
+            # what the allocator hands out next holds NaN: a kernel that reads 32-bit sums which no CTA of its launch wrote shows it
+            for size in range(1, 17):
+                junk = torch.full((size, tokens, heads * dv), float("nan"), dtype=torch.float32, device=device)
+                del junk
             if tiles:
                 ops.pooled_attention(q, token_pages, pool_pages, out, tiles=as_int([v for tile in tiles for v in tile]), num_tiles=len(tiles), shares=shares, **common)
+            for size in range(1, 17):
+                junk = torch.full((size, tokens, heads * dv), float("nan"), dtype=torch.float32, device=device)
+                del junk
             if singles:
                 ops.pooled_attention_single(q, token_pages, pool_pages, out, singles=as_int(singles), num_singles=len(singles), shares=shares, **common)
         else:
